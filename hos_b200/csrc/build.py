@@ -19,7 +19,7 @@ Libraries and what needs them:
   gemm_skinny bfloat16 models: the matrix product for up to 16 rows (decoding)
   blocks      models built from the other kinds of block: the hashed token-pair embedding, the
               parallel block's add-and-norms, attention over a latent cache, the matrix-state
-              recurrence, the routed feed-forward
+              recurrence, the routed feed-forward, the norm without statistics (Dynamic Tanh)
   mixers      models with a norm after the residual sum, attention with a sink, chunks and a gate per
               head over keys and values of unequal sizes, and the matrix-state recurrences with a
               decay per head (constant, or per token with the delta rule and short convolutions)
@@ -49,7 +49,7 @@ _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "slot_state.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
-    "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu"], []),
+    "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu", "dyt_norm.cu"], []),
     "mixers": (["postnorm.cu", "gated_attention.cu", "gated_attention_mma.cu", "state_scan.cu"], []),
 }
 

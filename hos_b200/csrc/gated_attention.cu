@@ -1,16 +1,20 @@
-// Softmax attention whose keys and values may differ in size, with per-head query/key norms, a partial
-// rotation with scaled frequencies, a mask of chunks or of a window, a sink in the denominator and a gate
-// per head.  Everything between the projections and the output projection is 32-bit arithmetic.
+// Softmax attention whose keys and values may differ in size, with query/key norms (per head, or over the whole
+// projection), a partial rotation with scaled frequencies, a mask of chunks or of a window (which may keep a
+// sequence's first keys in sight), a sink in the denominator and a gate per head.  Everything between the
+// projections and the output projection is 32-bit arithmetic.
 //
 // qk_prep: one block per token over the fused projection row [q | k | v | gate logits] (32-bit, biases added
 //   here): each query and key head is divided by its root mean square and multiplied by a weight shared by
-//   the heads, its first rot_dims numbers are rotated as neighbouring pairs (2i, 2i+1) by the angle
-//   position * freq[i], cosine and sine times `magnitude`; queries are written as 32-bit rows, keys and values
-//   (in the cache's type) to their places in the paged cache.
+//   the heads (norm_whole: the root mean square is taken over all query heads, and over all key heads, at once,
+//   and the weight has a number per column), its first rot_dims numbers are rotated as neighbouring pairs
+//   (2i, 2i+1) by the angle position * freq[i], cosine and sine times `magnitude`; queries are written as 32-bit
+//   rows, keys and values (in the cache's type) to their places in the paged cache.  With v_first the values
+//   are first blended with another layer's values of the same token, v <- (1 - v_mix) v + v_mix v_first, and the
+//   blend is what the cache holds.
 // gated_attn: one warp per (token, up to 8 query heads that share a kv head, share of the keys).  A lane takes a
 //   key: 32 scores per head at a time, then the lanes turn to the value columns; a key or value row is read once
 //   for all of the warp's heads.  Keys j of position i: j <= i and, with chunks of size C,
-//   floor(j / C) = floor(i / C); with a window W, j > i - W.  The denominator also holds exp(sink[head]).
+//   floor(j / C) = floor(i / C); with a window W, j > i - W or j < keep_first.  The denominator also holds exp(sink[head]).
 //   The head's output is multiplied by the logistic function of its gate logit.  With more than one share the
 //   partial (maximum, sum, weighted values) go to a workspace and attn_merge adds them.
 #include "common.cuh"
@@ -37,8 +41,10 @@ __global__ void __launch_bounds__(128)
 qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias, const float* __restrict__ q_norm,
                const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims, float magnitude,
                const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-               float* __restrict__ q_out, PagedKV2 cache, int H, int G, int kd, int vd) {
+               float* __restrict__ q_out, PagedKV2 cache, int H, int G, int kd, int vd, int norm_whole,
+               const float* __restrict__ v_first, long long v_first_ld, float v_mix) {
     pdl_enter();
+    __shared__ float scratch[32];
     const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = token_seq[n];
     const float* row = proj + (size_t)n * ld;
@@ -51,11 +57,25 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
     const int slot = seq_slot[seq];
     const int page = G > 0 ? cache.page_table[(size_t)slot * cache.table_stride + table_entry(cache, pos / kPageTokens)] : 0;
     const int r = pos % kPageTokens;
+    float inv_all[2] = {0.f, 0.f};                       // norm_whole: one root mean square for all q heads, one for all k heads
+    if (norm_whole) {
+        for (int part = 0; part < (G > 0 ? 2 : 1); ++part) {
+            const int c0 = part == 0 ? 0 : H * kd, cn = part == 0 ? H * kd : G * kd;
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < cn; i += blockDim.x) {
+                const float x = row[c0 + i] + (bias ? bias[c0 + i] : 0.f);
+                ss = fmaf(x, x, ss);
+            }
+            ss = block_sum(ss, scratch);
+            inv_all[part] = 1.f / sqrtf(ss / (float)cn + eps);
+        }
+    }
     // query heads 0..H-1, then key heads H..H+G-1
     for (int item = warp; item < H + G; item += 4) {
         const bool is_q = item < H;
         const int col0 = item * kd;                      // q heads and k heads follow one another in the row
         const float* nw = is_q ? q_norm : k_norm;
+        if (nw != nullptr && norm_whole) nw += (is_q ? item : item - H) * kd;
         float v[kPrepPL];
         float ss = 0.f;
 #pragma unroll
@@ -66,7 +86,7 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
         }
         if (nw != nullptr) {
             ss = warp_sum(ss);
-            const float inv = 1.f / sqrtf(ss / (float)kd + eps);
+            const float inv = norm_whole ? inv_all[is_q ? 0 : 1] : 1.f / sqrtf(ss / (float)kd + eps);
 #pragma unroll
             for (int i = 0; i < kPrepPL; ++i) {
                 const int d = lane + 32 * i;
@@ -107,7 +127,9 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
         for (int i = threadIdx.x; i < G * vd; i += blockDim.x) {
             const int g = i / vd, d = i % vd;
             TC* vp = (TC*)cache.v_pages + ((size_t)page * G + g) * (size_t)kPageTokens * vd;
-            vp[kv_elem_offset(r, d, vd)] = from_float<TC>(row[col0 + i] + (bias ? bias[col0 + i] : 0.f));
+            float x = row[col0 + i] + (bias ? bias[col0 + i] : 0.f);
+            if (v_first != nullptr) x = fmaf(v_mix, v_first[(size_t)n * v_first_ld + i], (1.f - v_mix) * x);
+            vp[kv_elem_offset(r, d, vd)] = from_float<TC>(x);
         }
     }
 }
@@ -136,7 +158,7 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
                   long long gate_stride, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                   const int* __restrict__ seq_slot, void* __restrict__ out, int out_bf16, float* __restrict__ part_acc,
                   float* __restrict__ part_ml, int n_splits, int n_tokens, int H, int G, int kd, int vd, float scale,
-                  int chunk, int window) {
+                  int chunk, int window, int keep_first) {
     pdl_enter();
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -162,10 +184,13 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
     }
     const int pos = token_pos[n];
     const int g = h0 / (H / G);
-    int lo = 0;
-    if (chunk > 0) lo = pos / chunk * chunk;
-    if (window > 0) lo = max(lo, pos + 1 - window);
-    int hi = pos + 1;
+    int first = 0;
+    if (chunk > 0) first = pos / chunk * chunk;
+    if (window > 0) first = max(first, pos + 1 - window);
+    // the keys a row sees, counted u = 0, 1, ...: the sequence's first `kept` keys (those of the first keep_first that the
+    // mask's lower edge has passed), then the keys first .. pos; key_of(u) is the position of the u-th
+    const int kept = min(max(keep_first, 0), first), shift = first - kept;
+    int lo = 0, hi = kept + pos + 1 - first;
     if (n_splits > 1) {       // shares are runs of whole blocks of 32 keys
         const int blocks = (hi - lo + 31) / 32, per = (blocks + n_splits - 1) / n_splits;
         const int a = lo + split * per * 32;
@@ -192,12 +217,12 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
     const bool vec = (kd & 7) == 0;
 
     for (int t0 = lo; t0 < hi; t0 += 32) {
-        const int t = t0 + lane;
+        const int u = t0 + lane, t = u < kept ? u : u + shift;
         float s[QH];
 #pragma unroll
         for (int hh = 0; hh < QH; ++hh) s[hh] = -INFINITY;
         int my_page = 0;
-        if (t < hi) {
+        if (u < hi) {
             my_page = table[table_entry(cache, t / kPageTokens)];
             const int r = t % kPageTokens;
             const TC* kp = (const TC*)cache.k_pages + ((size_t)my_page * G + g) * (size_t)kPageTokens * kd;
@@ -228,7 +253,7 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
         for (int hh = 0; hh < QH; ++hh) {
             const float m_new = fmaxf(m[hh], warp_max(s[hh]));
             const float corr = expf(m[hh] - m_new);          // m_new is finite here: the block holds one key at least
-            p[hh] = t < hi ? expf(s[hh] - m_new) : 0.f;
+            p[hh] = u < hi ? expf(s[hh] - m_new) : 0.f;
             l[hh] = l[hh] * corr + warp_sum(p[hh]);
 #pragma unroll
             for (int i = 0; i < VPL; ++i) acc[hh][i] *= corr;
@@ -237,7 +262,7 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
         const int cnt = min(32, hi - t0);
         for (int j = 0; j < cnt; ++j) {
             const int pg = __shfl_sync(0xffffffffu, my_page, j);
-            const int r = (t0 + j) % kPageTokens;
+            const int r = (t0 + j < kept ? t0 + j : t0 + j + shift) % kPageTokens;
             const TC* vp = (const TC*)cache.v_pages + ((size_t)pg * G + g) * (size_t)kPageTokens * vd;
             float vv[VPL];
 #pragma unroll
@@ -319,12 +344,13 @@ using namespace hos;
 
 // proj: float32 [N][ld], columns q (H * kd), then k (G * kd) and v (G * vd) if G > 0 (a call that reads another
 // call's cache passes G = 0 and projects neither), then whatever else the caller keeps there.  bias: the same
-// columns' biases or null.  q_norm / k_norm: [kd] or null.  freq: [rot_dims / 2] or null.
+// columns' biases or null.  q_norm / k_norm: [kd] or null (norm_whole: [H * kd] and [G * kd]).  freq: [rot_dims / 2] or
+// null.  v_first: row n's values of another layer at v_first[n * v_first_ld + ...] (G * vd numbers), or null.
 extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const float* q_norm, const float* k_norm, float eps,
                            const float* freq, int rot_dims, float magnitude, const int* token_pos, const int* token_seq,
                            const int* seq_slot, float* q_out, void* k_pages, void* v_pages, int cache_dtype,
                            const int* page_table, int table_stride, int ring_pages, int N, int H, int G, int kd, int vd,
-                           cudaStream_t stream) {
+                           int norm_whole, const float* v_first, long long v_first_ld, float v_mix, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (kd <= 0 || kd > 32 * kPrepMaxPL) HOS_REFUSE("qk_prep: heads of %d numbers are outside 1..%d", kd, 32 * kPrepMaxPL);
     if (freq == nullptr) rot_dims = 0;
@@ -332,7 +358,7 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
     PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
 #define HOS_QKP(TC, PL)                                                                                              \
     launch_pdl(qk_prep_kernel<TC, PL>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims, \
-               magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd)
+               magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd, norm_whole, v_first, v_first_ld, v_mix)
 #define HOS_QKP_T(TC)                                                                                                \
     do {                                                                                                             \
         if (kd <= 32) HOS_QKP(TC, 1);                                                                                \
@@ -349,13 +375,14 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
 }
 
 // q: float32 [N][H][kd].  out: [N][H][vd] of out_dtype.  gate: row n's logit of head h at gate[n * gate_stride + h], or
-// null.  sink: [H] or null.  chunk, window: 0 for none.  n_splits > 1: part_acc [N][H][n_splits][vd] and part_ml
+// null.  sink: [H] or null.  chunk, window: 0 for none; keep_first: with a window, that many of a sequence's first keys
+// stay in sight.  n_splits > 1: part_acc [N][H][n_splits][vd] and part_ml
 // [N][H][n_splits][2] float32 must be given.
 extern "C" int hos_gated_attn(const float* q, void* k_pages, void* v_pages, int cache_dtype, const int* page_table,
                               int table_stride, int ring_pages, const float* sink, const float* gate, long long gate_stride,
                               const int* token_pos, const int* token_seq, const int* seq_slot, void* out, int out_dtype,
                               float* part_acc, float* part_ml, int n_splits, int N, int H, int G, int kd, int vd, float scale,
-                              int chunk, int window, cudaStream_t stream) {
+                              int chunk, int window, int keep_first, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (G <= 0 || H % G != 0) HOS_REFUSE("gated_attn: %d heads are not a multiple of %d kv heads", H, G);
     if (vd <= 0 || vd > 32 * kMaxVPL) HOS_REFUSE("gated_attn: value heads of %d numbers are outside 1..%d", vd, 32 * kMaxVPL);
@@ -378,7 +405,7 @@ extern "C" int hos_gated_attn(const float* q, void* k_pages, void* v_pages, int 
 #define HOS_GA(TC, VPL, QH)                                                                                          \
     launch_pdl(gated_attn_kernel<TC, VPL, QH>, dim3(blocks), dim3(kAttnWarps * 32), smem, stream, q, c, sink, gate,  \
                gate_stride, token_pos, token_seq, seq_slot, out, out_bf16, part_acc, part_ml, n_splits, N, H, G, kd, vd, \
-               scale, chunk, window)
+               scale, chunk, window, keep_first)
 #define HOS_GA_Q(TC, VPL)                                                                                            \
     do {                                                                                                             \
         if (qh == 8) { if constexpr (VPL <= 4) HOS_GA(TC, VPL, 8); }                                                 \

@@ -5,7 +5,7 @@
 // positions are pages of the cache, copied as they lie (the cache's permutation of 16-byte groups is the one the
 // kernel reads with) through a two-stage cp.async pipeline.  Per tile each warp computes S = Q K^T for its 16
 // queries (m16n8k16, 32-bit accumulators: with bfloat16 operands every product is exact, so the scores are 32-bit
-// sums), scales, masks (causal; the chunk's first key; the window's edge), keeps the running maximum and sum in
+// sums), scales, masks (causal; the chunk's first key; the window's edge, with or without a sequence's kept first keys), keeps the running maximum and sum in
 // 32-bit and accumulates O += P V with the 32-bit weights P fed as two bfloat16 terms (P = hi + lo, 16 bits of
 // mantissa) so that the weights are not rounded to 8 bits.  The sink starts the running maximum and the sum
 // (exp(sink - max) counts once); the head's gate multiplies the output.  Keys of KD and values of VD numbers,
@@ -30,7 +30,7 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
                       const int* __restrict__ page_table, int table_stride, int ring_pages, const float* __restrict__ sink,
                       const float* __restrict__ gate, long long gate_stride, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-                      bf16* __restrict__ out, int n_seqs, int H, int G, float scale, int chunk, int window) {
+                      bf16* __restrict__ out, int n_seqs, int H, int G, float scale, int chunk, int window, int keep_first) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [64][KD]
@@ -56,7 +56,10 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
     int first_key = chunk > 0 ? p0 / chunk * chunk : 0;
     if (window > 0) first_key = max(first_key, p0 + 1 - window);
     const int kt_lo = first_key / MK, kt_hi = last_q / MK;
-    const int n_kt = kt_hi - kt_lo + 1;
+    // with kept first keys, their tiles come first (those that lie before the mask's own first tile)
+    const int n_keep = keep_first > 0 ? min((keep_first + MK - 1) / MK, kt_lo) : 0;
+    const int n_kt = n_keep + kt_hi - kt_lo + 1;
+    auto tile_of = [&](int it) { return it < n_keep ? it : kt_lo + it - n_keep; };
     const int* table = page_table + (size_t)seq_slot[seq] * table_stride;
 
     // the queries: 32-bit rows, rounded here to the tensor cores' type; rows beyond the sequence are zeros
@@ -80,7 +83,7 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
         for (int i = threadIdx.x; i < MK * (KD / 8); i += 128) cp16(ks + i * 8, ksrc + i * 8);
         for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
     };
-    load_kv(kt_lo, 0);
+    load_kv(tile_of(0), 0);
     cp_commit();
 
     const float sk = sink != nullptr ? sink[head] : -INFINITY;
@@ -100,13 +103,13 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
 
     for (int it = 0; it < n_kt; ++it) {
         const int stage = it & 1;
-        if (it + 1 < n_kt) load_kv(kt_lo + it + 1, stage ^ 1);
+        if (it + 1 < n_kt) load_kv(tile_of(it + 1), stage ^ 1);
         cp_commit();
         cp_wait<1>();
         __syncthreads();
         const uint32_t k_base = smem_u32(kv_s + (size_t)stage * kStage);
         const uint32_t v_base = k_base + 2 * MK * KD;
-        const int key0 = (kt_lo + it) * MK;
+        const int key0 = tile_of(it) * MK;
 
         float sc[8][4];
 #pragma unroll
@@ -133,7 +136,7 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
-                const bool vis = key <= qpos[i >> 1] && key >= qlo[i >> 1];
+                const bool vis = key <= qpos[i >> 1] && (key >= qlo[i >> 1] || key < keep_first);
                 const float s = vis ? sc[nt][i] * scale : -INFINITY;
                 sc[nt][i] = s;
                 m_new[i >> 1] = fmaxf(m_new[i >> 1], s);
@@ -220,7 +223,8 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
                              const float* __restrict__ sink, const float* __restrict__ gate, long long gate_stride,
                              const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                              const int* __restrict__ seq_slot, bf16* __restrict__ out, float* __restrict__ part_acc,
-                             float* __restrict__ part_ml, int n_splits, int H, int G, float scale, int chunk, int window) {
+                             float* __restrict__ part_ml, int n_splits, int H, int G, float scale, int chunk, int window,
+                             int keep_first) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][KD]
@@ -244,10 +248,15 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
     const int pos = token_pos[n];
     int lo = chunk > 0 ? pos / chunk * chunk : 0;
     if (window > 0) lo = max(lo, pos + 1 - window);
-    const int kt_first = lo / MK, n_all = pos / MK - kt_first + 1;
+    // the tiles a row sees, counted 0, 1, ...: the tiles of the kept first keys (those before the mask's own first
+    // tile), then the mask's tiles; the shares are runs of that count
+    const int kt_first = lo / MK;
+    const int n_keep = keep_first > 0 ? min((keep_first + MK - 1) / MK, kt_first) : 0;
+    const int n_all = n_keep + pos / MK - kt_first + 1;
     const int per = (n_all + n_splits - 1) / n_splits;
-    const int kt_lo = kt_first + split * per;
-    const int n_kt = min(per, kt_first + n_all - kt_lo);
+    const int kt_lo = split * per;
+    const int n_kt = min(per, n_all - kt_lo);
+    auto tile_of = [&](int i) { return i < n_keep ? i : kt_first + i - n_keep; };
     if (n_kt <= 0) {                                                // a share without tiles (never the first)
         for (int i = threadIdx.x; i < QH; i += 128) {
             const size_t pi = ((size_t)n * H + h0 + i) * n_splits + split;
@@ -277,7 +286,7 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
         for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
     };
     for (int s = 0; s < kDecStages - 1; ++s) {                      // the first tiles are on their way before anything else
-        if (s < n_kt) load_kv(kt_lo + s, s);
+        if (s < n_kt) load_kv(tile_of(kt_lo + s), s);
         cp_commit();
     }
 
@@ -297,13 +306,13 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
 
     for (int it = 0; it < n_kt; ++it) {
         const int stage = it % kDecStages;
-        if (it + kDecStages - 1 < n_kt) load_kv(kt_lo + it + kDecStages - 1, (it + kDecStages - 1) % kDecStages);
+        if (it + kDecStages - 1 < n_kt) load_kv(tile_of(kt_lo + it + kDecStages - 1), (it + kDecStages - 1) % kDecStages);
         cp_commit();
         cp_wait<kDecStages - 1>();
         __syncthreads();
         const uint32_t k_base = smem_u32(kv_s + (size_t)stage * kStage);
         const uint32_t v_base = k_base + 2 * MK * KD;
-        const int key0 = (kt_lo + it) * MK + warp * 16;             // this warp's 16 keys of the tile
+        const int key0 = tile_of(kt_lo + it) * MK + warp * 16;             // this warp's 16 keys of the tile
 
         float sc[2][4];
 #pragma unroll
@@ -322,7 +331,7 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
-                const float s = (key <= pos && key >= lo) ? sc[nt][i] * scale : -INFINITY;
+                const float s = (key <= pos && (key >= lo || key < keep_first)) ? sc[nt][i] * scale : -INFINITY;
                 sc[nt][i] = s;
                 m_new[i >> 1] = fmaxf(m_new[i >> 1], s);
             }
@@ -425,7 +434,7 @@ extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const voi
                                   int table_stride, int ring_pages, const float* sink, const float* gate,
                                   long long gate_stride, const int* cu_seqlens, const int* token_pos, const int* token_seq,
                                   const int* seq_slot, void* out, int n_seqs, int n_q_tiles, int H, int G, int kd, int vd,
-                                  float scale, int chunk, int window, cudaStream_t stream) {
+                                  float scale, int chunk, int window, int keep_first, cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
     if (G <= 0 || H % G != 0 || H > 65535) HOS_REFUSE("gated_attn_mma: %d heads over %d kv heads", H, G);
     if ((kd != 64 && kd != 128) || (vd != 64 && vd != 128))
@@ -443,7 +452,7 @@ extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const voi
         }                                                                                                            \
         launch_pdl(gated_attn_mma_kernel<KDv, VDv>, grid, dim3(128), smem, stream, q, (const bf16*)k_pages,          \
                    (const bf16*)v_pages, page_table, table_stride, ring_pages, sink, gate, gate_stride, cu_seqlens,  \
-                   token_pos, token_seq, seq_slot, (bf16*)out, n_seqs, H, G, scale, chunk, window);                  \
+                   token_pos, token_seq, seq_slot, (bf16*)out, n_seqs, H, G, scale, chunk, window, keep_first);      \
     } while (0)
     if (kd == 64 && vd == 64) HOS_GAM(64, 64);
     else if (kd == 64) HOS_GAM(64, 128);
@@ -460,7 +469,7 @@ extern "C" int hos_gated_attn_mma_decode(const float* q, const void* k_pages, co
                                          long long gate_stride, const int* token_pos, const int* token_seq,
                                          const int* seq_slot, void* out, float* part_acc, float* part_ml, int n_splits,
                                          int N, int H, int G, int kd, int vd, float scale, int chunk, int window,
-                                         cudaStream_t stream) {
+                                         int keep_first, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (G <= 0 || H % G != 0 || H / G > 16 || G > 65535) HOS_REFUSE("gated_attn_mma_decode: %d heads over %d kv heads", H, G);
     if ((kd != 64 && kd != 128) || (vd != 64 && vd != 128))
@@ -479,7 +488,8 @@ extern "C" int hos_gated_attn_mma_decode(const float* q, const void* k_pages, co
         }                                                                                                            \
         launch_pdl(gated_attn_mma_decode_kernel<KDv, VDv>, grid, dim3(128), smem, stream, q, (const bf16*)k_pages,   \
                    (const bf16*)v_pages, page_table, table_stride, ring_pages, sink, gate, gate_stride, token_pos,   \
-                   token_seq, seq_slot, (bf16*)out, part_acc, part_ml, n_splits, H, G, scale, chunk, window);        \
+                   token_seq, seq_slot, (bf16*)out, part_acc, part_ml, n_splits, H, G, scale, chunk, window,         \
+                   keep_first);                                                                                      \
     } while (0)
     if (kd == 64 && vd == 64) HOS_GAD(64, 64);
     else if (kd == 64) HOS_GAD(64, 128);

@@ -1,18 +1,21 @@
 // A routed feed-forward (mixture of experts) whose whole step stays on the device.
 //
-//   route     per row: router logits in 32-bit, softmax over all outputs, the `top` largest of
-//             (score + correction) chosen, each weighted by its plain score (not renormalised).
+//   route     per row: router logits in 32-bit, scores = softmax over all outputs (or, scoring 1, the logistic
+//             function of each logit), the `top` largest of (score + correction) chosen, each weighted by
+//             its plain score (not renormalised).
 //             The last `n_identity` router outputs are experts without tensors: their output is
 //             the row itself.
 //   align     the chosen (row, choice) pairs listed expert by expert, each expert's list padded to
 //             whole tiles of kTile rows, and the expert of every tile.
 //   gate_up   per tile, the expert's gate and up products of the listed rows and the activation
 //             y = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
-//             (limit <= 0: no clamp).
+//             (limit <= 0: no clamp; the 1 is `up_shift`, 0 for the plain gated form g' sigmoid(alpha g') u').  With
+//             in_weight the pair's weight multiplies the expert's INPUT: gate and up products are linear, so
+//             g and u are multiplied by it before the activation, and down takes no weight.
 //   down      per tile, the expert's down product, times the pair's weight, to the pair's own row
 //             of a 32-bit buffer.
 //   combine   per row, the sum of its pairs' rows in the order of the choices, identity experts added
-//             as weight * row.
+//             as weight * row, plus the row of `extra` if given (an expert that every row uses).
 // The grid of the tiled kernels is the most tiles the step can have; tiles beyond the real ones
 // leave at once, so nothing depends on the host knowing the counts.  Products accumulate in 32-bit;
 // a warp whose rows of a tile are all padding skips the arithmetic.
@@ -24,7 +27,8 @@ namespace hos {
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
                                  const float* __restrict__ correction, const int* __restrict__ token_seq,
-                                 int* __restrict__ choice, float* __restrict__ weight, int D, int n_out, int top) {
+                                 int* __restrict__ choice, float* __restrict__ weight, int D, int n_out, int top,
+                                 int scoring) {
     pdl_enter();
     extern __shared__ float z[];               // [n_out] scores, [n_out] taken flags, [warps][n_out] partial sums
     float* taken = z + n_out;
@@ -64,18 +68,22 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     }
     __syncthreads();
     if (warp != 0) return;
-    float m = -INFINITY;
-    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_out; e += 32) {
-        const float p = expf(z[e] - m);
-        z[e] = p;
-        sum += p;
+    if (scoring == 1) {
+        for (int e = lane; e < n_out; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < n_out; e += 32) {
+            const float p = expf(z[e] - m);
+            z[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < n_out; e += 32) z[e] = z[e] / sum;
     }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < n_out; e += 32) z[e] = z[e] / sum;
     __syncwarp();
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -152,7 +160,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ W, const int* __restrict__ listed,
                    const int* __restrict__ tile_expert, T* __restrict__ y, int D, int F, int top, float limit,
-                   float alpha) {
+                   float alpha, float up_shift, const float* __restrict__ in_weight) {
     pdl_enter();
     constexpr int BK = 16;
     __shared__ float As[BK][kTile + 4];
@@ -209,16 +217,17 @@ moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ W, const int* 
     for (int i = 0; i < 4; ++i) {
         const int r = ty * 4 + i;
         if (rows[r] < 0) continue;
+        const float wt = in_weight ? in_weight[listed[tile * kTile + r]] : 1.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= F) continue;
-            float g = acc_g[i][j], u = acc_u[i][j];
+            float g = acc_g[i][j] * wt, u = acc_u[i][j] * wt;
             if (limit > 0.f) {
                 g = fminf(g, limit);
                 u = fminf(fmaxf(u, -limit), limit);
             }
-            const float v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+            const float v = g / (1.f + expf(-alpha * g)) * (u + up_shift);
             y[(size_t)(tile * kTile + r) * F + n] = from_float<T>(v);
         }
     }
@@ -273,7 +282,7 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ W, const int* __r
     for (int i = 0; i < 4; ++i) {
         const int id = ids[ty * 4 + i];
         if (id < 0) continue;
-        const float wt = weight[id];
+        const float wt = weight ? weight[id] : 1.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
@@ -292,7 +301,7 @@ moe_down_kernel(const T* __restrict__ y, const T* __restrict__ W, const int* __r
 __global__ void __launch_bounds__(256)
 moe_gate_up_tc_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ listed,
                       const int* __restrict__ tile_expert, bf16* __restrict__ y, int D, int F, int top, float limit,
-                      float alpha) {
+                      float alpha, float up_shift, const float* __restrict__ in_weight) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char raw[];
     bf16* smem = reinterpret_cast<bf16*>(raw);
@@ -321,15 +330,16 @@ moe_gate_up_tc_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, co
         for (int half = 0; half < 2; ++half) {
             const int r = warp_m * 16 + (lane >> 2) + half * 8;
             if (rows[r] < 0) continue;
+            const float wt = in_weight ? in_weight[listed[tile * kTile + r]] : 1.f;
             float v[2];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                float g = acc[0][nt][half * 2 + c], u = acc[1][nt][half * 2 + c];
+                float g = acc[0][nt][half * 2 + c] * wt, u = acc[1][nt][half * 2 + c] * wt;
                 if (limit > 0.f) {
                     g = fminf(g, limit);
                     u = fminf(fmaxf(u, -limit), limit);
                 }
-                v[c] = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+                v[c] = g / (1.f + expf(-alpha * g)) * (u + up_shift);
             }
             *reinterpret_cast<uint32_t*>(y + (size_t)(tile * kTile + r) * F + n) = pack_bf16(v[0], v[1]);
         }
@@ -361,7 +371,7 @@ moe_down_tc_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const
     for (int half = 0; half < 2; ++half) {
         const int id = ids[warp_m * 16 + (lane >> 2) + half * 8];
         if (id < 0) continue;
-        const float wt = weight[id];
+        const float wt = weight ? weight[id] : 1.f;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
             const int n = n0 + warp_n * 32 + nt * 8 + (lane & 3) * 2;
@@ -393,7 +403,8 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
 // y[pair][F] = act(gate, up) of row pair / top under expert choice[pair]
 __global__ void __launch_bounds__(256)
 moe_gate_up_few_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ choice,
-                       bf16* __restrict__ y, int D, int F, int top, int n_experts, float limit, float alpha) {
+                       bf16* __restrict__ y, int D, int F, int top, int n_experts, float limit, float alpha,
+                       float up_shift, const float* __restrict__ in_weight) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char raw[];
     uint4* row = reinterpret_cast<uint4*>(raw);                 // the activation row, 8 numbers a group
@@ -419,11 +430,15 @@ moe_gate_up_few_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, c
         sg = warp_sum(sg);
         su = warp_sum(su);
         if (lane == 0) {
+            if (in_weight) {
+                sg *= in_weight[pair];
+                su *= in_weight[pair];
+            }
             if (limit > 0.f) {
                 sg = fminf(sg, limit);
                 su = fminf(fmaxf(su, -limit), limit);
             }
-            y[(size_t)pair * F + f] = from_float<bf16>(sg / (1.f + expf(-alpha * sg)) * (su + 1.f));
+            y[(size_t)pair * F + f] = from_float<bf16>(sg / (1.f + expf(-alpha * sg)) * (su + up_shift));
         }
     }
 }
@@ -442,7 +457,7 @@ moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, cons
     for (int g = threadIdx.x; g < groups; g += 256) row[g] = src[g];
     __syncthreads();
     const bf16* Wd = W + (size_t)e * D * F;
-    const float wt = weight[pair];
+    const float wt = weight ? weight[pair] : 1.f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int n = blockIdx.x * kFewFeatures + warp * 4 + q;
@@ -458,11 +473,11 @@ moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, cons
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice,
                                    const float* __restrict__ weight, const T* __restrict__ h, float* __restrict__ out,
-                                   int D, int top, int n_experts) {
+                                   int D, int top, int n_experts, const T* __restrict__ extra) {
     pdl_enter();
     const int n = blockIdx.x;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float s = 0.f;
+        float s = extra ? to_float(extra[(size_t)n * D + d]) : 0.f;
         for (int k = 0; k < top; ++k) {
             const size_t id = (size_t)n * top + k;
             const int e = choice[id];
@@ -481,17 +496,17 @@ extern "C" int hos_moe_tile_rows() { return kTile; }
 
 extern "C" int hos_moe_route(const void* h, int dtype, const float* router, const float* correction,
                              const int* token_seq, int* choice, float* weight, int N, int D, int n_out, int top,
-                             cudaStream_t stream) {
+                             int scoring, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (top <= 0 || top > n_out) HOS_REFUSE("moe_route: %d of %d router outputs cannot be chosen", top, n_out);
     const size_t smem = (size_t)(2 + 8) * n_out * sizeof(float);       // scores, flags, and a partial sum per warp (8 warps)
     if (smem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
     if (dtype == kBF16)
         launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, (const bf16*)h, router, correction, token_seq,
-                   choice, weight, D, n_out, top);
+                   choice, weight, D, n_out, top, scoring);
     else if (dtype == kF32)
         launch_pdl(moe_route_kernel<float>, dim3(N), dim3(256), smem, stream, (const float*)h, router, correction, token_seq,
-                   choice, weight, D, n_out, top);
+                   choice, weight, D, n_out, top, scoring);
     else
         HOS_REFUSE("moe_route: unknown dtype %d", dtype);
     return check_launch("moe_route");
@@ -508,8 +523,8 @@ extern "C" int hos_moe_align(const int* choice, int n_pairs, int n_experts, int*
 }
 
 extern "C" int hos_moe_gate_up(const void* h, const void* W, int dtype, const int* listed, const int* tile_expert,
-                               void* y, int max_tiles, int D, int F, int top, float limit, float alpha,
-                               cudaStream_t stream) {
+                               void* y, int max_tiles, int D, int F, int top, float limit, float alpha, float up_shift,
+                               const float* in_weight, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((F + kTile - 1) / kTile, max_tiles);
     if (grid.y > 65535) HOS_REFUSE("moe_gate_up: %d tiles are more than one launch takes", max_tiles);
@@ -520,13 +535,13 @@ extern "C" int hos_moe_gate_up(const void* h, const void* W, int dtype, const in
             set = true;
         }
         launch_pdl(moe_gate_up_tc_kernel, grid, dim3(256), (size_t)TcTile<2>::kSmemBytes, stream, (const bf16*)h,
-                   (const bf16*)W, listed, tile_expert, (bf16*)y, D, F, top, limit, alpha);
+                   (const bf16*)W, listed, tile_expert, (bf16*)y, D, F, top, limit, alpha, up_shift, in_weight);
     } else if (dtype == kBF16)
         launch_pdl(moe_gate_up_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, (const bf16*)W, listed, tile_expert,
-                   (bf16*)y, D, F, top, limit, alpha);
+                   (bf16*)y, D, F, top, limit, alpha, up_shift, in_weight);
     else if (dtype == kF32)
         launch_pdl(moe_gate_up_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, (const float*)W, listed,
-                   tile_expert, (float*)y, D, F, top, limit, alpha);
+                   tile_expert, (float*)y, D, F, top, limit, alpha, up_shift, in_weight);
     else
         HOS_REFUSE("moe_gate_up: unknown dtype %d", dtype);
     return check_launch("moe_gate_up");
@@ -557,14 +572,14 @@ extern "C" int hos_moe_down(const void* y, const void* W, int dtype, const int* 
 }
 
 extern "C" int hos_moe_combine(const float* pair_out, const int* choice, const float* weight, const void* h, int dtype,
-                               float* out, int N, int D, int top, int n_experts, cudaStream_t stream) {
+                               float* out, int N, int D, int top, int n_experts, const void* extra, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (dtype == kBF16)
         launch_pdl(moe_combine_kernel<bf16>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const bf16*)h, out, D,
-                   top, n_experts);
+                   top, n_experts, (const bf16*)extra);
     else if (dtype == kF32)
         launch_pdl(moe_combine_kernel<float>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const float*)h, out,
-                   D, top, n_experts);
+                   D, top, n_experts, (const float*)extra);
     else
         HOS_REFUSE("moe_combine: unknown dtype %d", dtype);
     return check_launch("moe_combine");
@@ -573,12 +588,13 @@ extern "C" int hos_moe_combine(const float* pair_out, const int* choice, const f
 // The same two products for a handful of pairs (see the kernels): y is [pairs][F] by pair id.  Returns 1 (and
 // launches nothing) where the sizes are not the kernels' (K no multiple of 8, rows that do not fit shared memory).
 extern "C" int hos_moe_gate_up_few(const void* h, const void* W, const int* choice, void* y, int n_pairs, int D, int F,
-                                   int top, int n_experts, float limit, float alpha, cudaStream_t stream) {
+                                   int top, int n_experts, float limit, float alpha, float up_shift, const float* in_weight,
+                                   cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (D % 8 || F % 8 || D * 2 > 96 * 1024 || ((uintptr_t)h | (uintptr_t)W | (uintptr_t)y) % 16) return 1;
     if (D * 2 > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 2);
     launch_pdl(moe_gate_up_few_kernel, dim3((F + kFewFeatures - 1) / kFewFeatures, n_pairs), dim3(256), (size_t)D * 2, stream,
-               (const bf16*)h, (const bf16*)W, choice, (bf16*)y, D, F, top, n_experts, limit, alpha);
+               (const bf16*)h, (const bf16*)W, choice, (bf16*)y, D, F, top, n_experts, limit, alpha, up_shift, in_weight);
     return check_launch("moe_gate_up_few");
 }
 

@@ -680,12 +680,15 @@ def moe_tile_rows() -> int:
     return _moe_tile
 
 
-def moe_route(h, router, correction, token_seq, choice, weight, top: int) -> None:
+MOE_SCORING = {"softmax": 0, "logistic": 1}
+
+
+def moe_route(h, router, correction, token_seq, choice, weight, top: int, scoring: int = 0) -> None:
     _check(h, "rows", None, 2)
     _check(router, "router", torch.float32, 2)
     n, d = h.shape
     blocks().call("hos_moe_route", _ptr(h), dtype_code(h.dtype), _ptr(router), _ptr(correction), _ptr(token_seq),
-                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), _stream())
+                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), int(scoring), _stream())
 
 
 def moe_align(choice, n_experts: int, listed, tile_expert) -> None:
@@ -693,10 +696,13 @@ def moe_align(choice, n_experts: int, listed, tile_expert) -> None:
                   _ptr(tile_expert), tile_expert.numel(), _stream())
 
 
-def moe_gate_up(h, w, listed, tile_expert, y, top: int, limit: float, alpha: float) -> None:
+def moe_gate_up(h, w, listed, tile_expert, y, top: int, limit: float, alpha: float, up_shift: float = 1.0,
+                in_weight: Optional[torch.Tensor] = None) -> None:
+    """in_weight ([pairs] float32): the pair's weight multiplies the expert's input (then `moe_down` takes none)."""
     _check(w, "expert gate/up weights", h.dtype, 3)
     blocks().call("hos_moe_gate_up", _ptr(h), _ptr(w), dtype_code(h.dtype), _ptr(listed), _ptr(tile_expert), _ptr(y),
-                  tile_expert.numel(), h.shape[1], w.shape[1] // 2, int(top), float(limit), float(alpha), _stream())
+                  tile_expert.numel(), h.shape[1], w.shape[1] // 2, int(top), float(limit), float(alpha), float(up_shift),
+                  _ptr(in_weight), _stream())
 
 
 def moe_down(y, w, listed, tile_expert, weight, pair_out) -> None:
@@ -705,18 +711,21 @@ def moe_down(y, w, listed, tile_expert, weight, pair_out) -> None:
                   _ptr(pair_out), tile_expert.numel(), w.shape[1], w.shape[2], _stream())
 
 
-def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_experts: int, limit: float, alpha: float) -> bool:
+def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_experts: int, limit: float, alpha: float,
+            up_shift: float = 1.0, weight_on_input: bool = False) -> bool:
     """Both expert products for a handful of (row, choice) pairs, without lists or tiles (decoding at small batch):
     y [pairs, F] and pair_out [pairs, D] by pair id.  False: the sizes are not these kernels' and nothing ran."""
     lib = blocks()
     global launch_count
     pairs, d, f = choice.numel(), h.shape[1], w_down.shape[2]
     rc = lib.fn("hos_moe_gate_up_few")(_ptr(h), _ptr(w_gate_up), _ptr(choice), _ptr(y), pairs, d, f, int(top), int(n_experts),
-                                       float(limit), float(alpha), _stream())
+                                       float(limit), float(alpha), float(up_shift),
+                                       _ptr(weight) if weight_on_input else None, _stream())
     if rc == 1:
         return False
     if rc == 0:
-        rc = lib.fn("hos_moe_down_few")(_ptr(y), _ptr(w_down), _ptr(choice), _ptr(weight), _ptr(pair_out), pairs, d, f,
+        rc = lib.fn("hos_moe_down_few")(_ptr(y), _ptr(w_down), _ptr(choice), None if weight_on_input else _ptr(weight),
+                                        _ptr(pair_out), pairs, d, f,
                                         int(n_experts), _stream())
     launch_count += 2
     if rc != 0:
@@ -725,10 +734,41 @@ def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_exper
     return True
 
 
-def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int) -> None:
+def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int, extra: Optional[torch.Tensor] = None) -> None:
+    """extra ([N, D] of h's type): added to every row (an expert that all rows use)."""
     n, d = h.shape
+    if extra is not None:
+        _check(extra, "the shared expert's output", h.dtype, 2)
+        if extra.shape != h.shape:
+            raise KernelError("moe_combine: the shared expert's output and the rows differ in size")
     blocks().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),
-                  n, d, int(top), int(n_experts), _stream())
+                  n, d, int(top), int(n_experts), _ptr(extra), _stream())
+
+
+def add_dyt(a: Optional[torch.Tensor], f: Optional[torch.Tensor], mult: float, x: torch.Tensor, alpha: float,
+            w: Optional[torch.Tensor], b: Optional[torch.Tensor], h: Optional[torch.Tensor]) -> None:
+    """x += mult * (a + f) (either may be absent; each [N, D] of any type or [parts, N, D] float32 partial sums); then,
+    if h is given, h = tanh(alpha * x) * w + b (h may be x itself)."""
+    _check(x, "residual stream", torch.float32, 2)
+    n, d = x.shape
+    parts = []
+    for t, what in ((a, "mixer output"), (f, "feed-forward output")):
+        if t is None:
+            parts.append(0)
+            continue
+        _check(t, what)
+        if t.dim() not in (2, 3) or tuple(t.shape[-2:]) != (n, d):
+            raise KernelError(f"add_dyt: {what} and the residual stream differ in size")
+        parts.append(t.shape[0] if t.dim() == 3 else 1)
+    if h is not None:
+        _check(h, "norm output", None, 2)
+        _check(w, "norm weight", torch.float32, 1)
+        _check(b, "norm bias", torch.float32, 1)
+        if h.shape != x.shape or w.shape[0] != d or b.shape[0] != d:
+            raise KernelError("add_dyt: sizes of the norm disagree")
+    blocks().call("hos_add_dyt", _ptr(a), dtype_code(a.dtype) if a is not None else 0, parts[0],
+                  _ptr(f), dtype_code(f.dtype) if f is not None else 0, parts[1], float(mult), _ptr(x), float(alpha),
+                  _ptr(w), _ptr(b), _ptr(h), dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
 
 
 # ---- a norm after the sum, gated attention with a sink, matrix-state scans (csrc/postnorm.cu, gated_attention.cu,
@@ -790,9 +830,12 @@ def group_norm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, gate_c
 
 def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
             eps: float, freq: Optional[torch.Tensor], rot_dims: int, magnitude: float, step, q_out: torch.Tensor,
-            cache: PagedKVArgs, n_heads: int, n_kv: int, kd: int, vd: int) -> None:
+            cache: PagedKVArgs, n_heads: int, n_kv: int, kd: int, vd: int, norm_whole: bool = False,
+            v_first: Optional[torch.Tensor] = None, v_first_col: int = 0, v_mix: float = 0.0) -> None:
     """proj: float32 [N, >= H kd + G (kd + vd)] = [q | k | v | ...] (G = n_kv; 0: a call that stores nothing).  Adds the
-    biases, norms and rotates the q and k heads, writes q_out float32 [N, H, kd] and stores k, v in the cache."""
+    biases, norms and rotates the q and k heads, writes q_out float32 [N, H, kd] and stores k, v in the cache.
+    norm_whole: one root mean square over all q heads and one over all k heads (weights [H kd], [G kd]).  v_first
+    (float32 [N, ld], the values from column v_first_col on): v <- (1 - v_mix) v + v_mix v_first before the store."""
     _check(proj, "projection rows", torch.float32, 2)
     _check(q_out, "queries", torch.float32, 3)
     n = proj.shape[0]
@@ -800,15 +843,25 @@ def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[t
         raise KernelError("qk_prep: sizes disagree")
     if n_kv and (cache.head_dim != kd or cache.v_dim != vd or cache.n_kv_heads != n_kv):
         raise KernelError("qk_prep: the cache does not fit the keys and values")
+    for wn, cols in ((q_norm, n_heads * kd), (k_norm, n_kv * kd)):
+        if wn is not None and wn.shape[0] != (cols if norm_whole else kd):
+            raise KernelError("qk_prep: a norm weight does not fit the heads")
+    vf_ptr, vf_ld = None, 0
+    if v_first is not None:
+        _check(v_first, "the other layer's values", torch.float32, 2)
+        if v_first.shape[0] != n or v_first_col + n_kv * vd > v_first.shape[1]:
+            raise KernelError("qk_prep: the other layer's values do not fit this layer's")
+        vf_ptr, vf_ld = ctypes.c_void_p(v_first.data_ptr() + 4 * v_first_col), v_first.shape[1]
     mixers().call("hos_qk_prep", _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freq),
                   int(rot_dims), float(magnitude), _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
                   _ptr(q_out), _ptr(cache.k_pages) if n_kv else None, _ptr(cache.v_pages) if n_kv else None,
                   dtype_code(cache.k_pages.dtype), _ptr(cache.page_table), cache.table_stride, cache.ring_pages, n,
-                  int(n_heads), int(n_kv), int(kd), int(vd), _stream())
+                  int(n_heads), int(n_kv), int(kd), int(vd), 1 if norm_whole else 0, vf_ptr, vf_ld, float(v_mix), _stream())
 
 
 def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-               gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_splits: int = 1) -> None:
+               gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_splits: int = 1,
+               keep_first: int = 0) -> None:
     """q: float32 [N, H, kd]; keys and values from the paged cache; out: [N, H * vd].  gate: float32 rows whose column
     gate_col + h is head h's gate logit."""
     _check(q, "queries", torch.float32, 3)
@@ -825,11 +878,12 @@ def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor]
                   ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
                   gate.shape[1] if gate is not None else 0, _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
                   _ptr(out), dtype_code(out.dtype), _ptr(part_acc), _ptr(part_ml), int(n_splits), n, heads,
-                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0), _stream())
 
 
 def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-                   gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_q_tiles: int) -> bool:
+                   gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int, n_q_tiles: int,
+                   keep_first: int = 0) -> bool:
     """The same attention on the tensor cores, for bfloat16 caches and rows that come many to a sequence.  False: the
     sizes are not that kernel's and nothing ran."""
     n, heads, kd = q.shape
@@ -843,13 +897,13 @@ def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Ten
                   ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
                   gate.shape[1] if gate is not None else 0, _ptr(step.cu_seqlens), _ptr(step.token_pos),
                   _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs), int(n_q_tiles), heads,
-                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+                  cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0), _stream())
     return True
 
 
 def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
                           gate_col: int, step, out: torch.Tensor, scale: float, chunk: int, window: int,
-                          n_splits: int = 1) -> bool:
+                          n_splits: int = 1, keep_first: int = 0) -> bool:
     """Single tokens on the tensor cores: the query heads that share a kv head are the rows of one tile.  False: the
     sizes are not that kernel's and nothing ran."""
     n, heads, kd = q.shape
@@ -867,7 +921,8 @@ def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[to
     mixers().call("hos_gated_attn_mma_decode", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
                   cache.table_stride, cache.ring_pages, _ptr(sink), gate_ptr, gate_ld, _ptr(step.token_pos),
                   _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), _ptr(part_acc), _ptr(part_ml), int(n_splits), n,
-                  heads, cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), _stream())
+                  heads, cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0),
+                  _stream())
     if n_splits > 1:
         mixers().call("hos_attn_merge", _ptr(part_acc), _ptr(part_ml), int(n_splits), gate_ptr, gate_ld,
                       _ptr(step.token_seq), _ptr(out), dtype_code(out.dtype), n, heads, vd, _stream())

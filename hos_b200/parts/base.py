@@ -20,7 +20,7 @@ product (`h`, `y`) has the runtime's compute dtype; logits are float32.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
@@ -36,6 +36,7 @@ class WeightSpec:
     role: str                        # "matrix", "vector" or "table"
     init_std: float                  # standard deviation of the random-weights mode
     fallback: Optional[str] = None   # another tensor to use when this one is absent (tied head)
+    optional: bool = False           # a checkpoint may lack it (a tensor that a format writes but this model does not use)
 
 
 @dataclass(frozen=True)
@@ -112,6 +113,8 @@ class StepInfo:
     tail_tokens: int = 0             # that many sequences, that many rows (a mixer may send them to another kernel)
     row_offset: int = 0              # of a part of a step (see rows()): its first row and its first sequence in the
     seq_offset: int = 0              # whole step, which cu_seqlens (rows) and token_seq, seq_slot (sequences) still count from
+    shared: dict = field(default_factory=dict)   # what one part of a step leaves for the parts that run after it in the same
+                                     # step (a layer's values that later layers blend into theirs); rows as the step's
 
     def fill_for(self, window: Optional[int]) -> float:
         """How full of keys the step's sequences are for a mixer with this window (None: all keys): the sum over

@@ -9,6 +9,8 @@ sums are 32-bit.
 "parallel": both branches read a norm (each its own weight) of the SAME x, and their sum is scaled,
     x += mult * (mixer(pre_mixer(x)) + ffn(pre_ffn(x)))
     (`mult`: the arrangement's own constant, LayerSpec.params["residual_mult"], default 1).
+"parallel_shared_norm": both branches read ONE norm of x,
+    h = pre(x);  x += mult * (mixer(h) + ffn(h))
 "postnorm": the norm comes after the sum, and the branches read the residual stream itself,
     x <- post_mixer(alpha * x + mixer(x));  x <- post_ffn(alpha * x + ffn(x))
     (`alpha`: LayerSpec.params["alpha"], default 1; a layer without a feed-forward has the first line only).
@@ -129,6 +131,31 @@ class ParallelLayer(Layer):
         return next_norm.forward(x) if next_norm is not None else None
 
 
+class SharedNormParallelLayer(Layer):
+    """h = pre(x); x += mult * (mixer(h) + ffn(h)): one norm, read by both branches.  Where the next norm (the next
+    layer's, or the model's last) can add and norm in one launch (`add_then`), the layer costs one row-wise launch;
+    any other norm is run after a plain sum.  A branch may hand back 32-bit partial sums, which that launch adds."""
+    norm_roles = ("pre",)
+    chains = True
+
+    def __init__(self, spec: LayerSpec, rt: Runtime):
+        super().__init__(spec, rt)
+        self.mult = float(spec.params.get("residual_mult", 1.0))
+
+    def entry_norm(self):
+        return self.norms["pre"]
+
+    def forward(self, x: torch.Tensor, step: StepInfo, store: CallStore, h_in=None, next_norm=None):
+        h = h_in if h_in is not None else self.norms["pre"].forward(x)
+        fused = hasattr(next_norm, "add_then")
+        a = self._branch(self.mixer, fused, h, step, store)
+        f = self._branch(self.feed_forward, fused, h, step)
+        if fused:
+            return next_norm.add_then(a, f, self.mult, x)
+        ops.scaled_add_norms(a, f, self.mult, x)
+        return next_norm.forward(x) if next_norm is not None else None
+
+
 class PostNormLayer(Layer):
     """x <- norm(alpha * x + branch(x)) for the mixer and then for the feed-forward.  The sum, the norm and the copy of
     the new x that the next branch's products read (or the model's last norm of it) are one kernel; x and the sums
@@ -180,4 +207,5 @@ class PostNormLayer(Layer):
 register_part("arrangement", "sandwich", SandwichLayer)
 register_part("arrangement", "postnorm", PostNormLayer)
 register_part("arrangement", "parallel", ParallelLayer)
+register_part("arrangement", "parallel_shared_norm", SharedNormParallelLayer)
 register_part("arrangement", "prenorm", PreNormLayer)

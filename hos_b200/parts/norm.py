@@ -52,6 +52,45 @@ class RMSNorm(Norm):
 register_part("norm", "rmsnorm", RMSNorm)
 
 
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * w + b: a norm that takes no mean and no variance (alpha one number, w and b a number
+    per column; 32-bit).  `forward(x, out=x)` norms the 32-bit rows in place."""
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.width = int(spec.params["width"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.alpha = 1.0
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return [WeightSpec(w["weight"], (self.width,), "vector", 0.1), WeightSpec(w["bias"], (self.width,), "vector", 0.1),
+                WeightSpec(w["alpha"], (), "vector", 0.1)]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        w = self.spec.weights
+        self.weight = self._vector32(tensors[w["weight"]])
+        self.bias = self._vector32(tensors[w["bias"]])
+        self.alpha = float(tensors[w["alpha"]].float().reshape(-1)[0].item())     # read once, here
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        ops.add_dyt(None, None, 0.0, x, self.alpha, self.weight, self.bias, out)
+        return out
+
+    def add_then(self, a, f, mult: float, x: torch.Tensor) -> torch.Tensor:
+        """x += mult * (a + f) and this norm of the new x, in one launch (a, f: rows or 32-bit partial sums, or None)."""
+        h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        ops.add_dyt(a, f, mult, x, self.alpha, self.weight, self.bias, h)
+        return h
+
+
+register_part("norm", "dynamic_tanh", DynamicTanh)
+
+
 class NormPair:
     """Two RMSNorms of the same row, from one kernel: what a block needs whose mixer and feed-forward both
     read a norm of the same residual stream.  `forward(x)` gives (first, second)."""

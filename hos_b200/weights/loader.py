@@ -43,6 +43,8 @@ def check_against(specs: Sequence[WeightSpec], source) -> Dict[str, str]:
         if name not in have:
             if s.fallback is not None and s.fallback in have:
                 name = s.fallback
+            elif s.optional:
+                continue
             else:
                 missing.append(s.name)
                 continue
