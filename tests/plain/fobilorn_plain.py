@@ -34,14 +34,14 @@ def silu(z):
 
 
 def embed(cfg, w, tokens):
-    big = cfg["embedding"]["bigram"]
+    big = cfg.get("embedding", {}).get("bigram")
     rows = []
     for t, tok in enumerate(tokens):
-        if t == 0:
-            r = big["buckets"]
-        else:
-            r = (tokens[t - 1] * big["mul_prev"] + tok * big["mul_cur"]) % big["buckets"]
-        rows.append(w["embed"][tok] + w["bigram"][r])
+        row = w["embed"][tok]
+        if big:
+            r = big["buckets"] if t == 0 else (tokens[t - 1] * big["mul_prev"] + tok * big["mul_cur"]) % big["buckets"]
+            row = row + w["bigram"][r]
+        rows.append(row)
     return dyt(torch.stack(rows), w, "embed.norm")
 
 
@@ -53,9 +53,9 @@ def visible(i: int, j: int, mask: Optional[dict]) -> bool:
     return i - j < mask["size"] or j < mask.get("keep_first", 0)
 
 
-def attention_mixer(m, eps, w, p, h, v_first, mixes: bool):
+def attention_mixer(m, eps, w, p, h, v_first, mixes: bool, sink: bool = True):
     """h: [T, width].  Returns (output [T, width], the values this layer made before mixing).  `mixes`: this layer
-    blends its values with `v_first`."""
+    blends its values with `v_first`.  `sink` False leaves the one out of the denominator (what a test compares with)."""
     T, H, G, d, vd = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]          # over all heads at once
     k = rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]
@@ -67,14 +67,13 @@ def attention_mixer(m, eps, w, p, h, v_first, mixes: bool):
     q, k, v = q.view(T, H, d), k.view(T, G, d), v.view(T, G, vd)
     gate = torch.sigmoid(h @ w[p + "g"].T)                    # [T, H]
     out = torch.zeros(T, H, vd, dtype=h.dtype)
-    for hd in range(H):
-        g = hd // (H // G)
-        for i in range(T):
-            js = [j for j in range(T) if visible(i, j, m.get("mask"))]
-            s = torch.stack([(q[i, hd] * k[j, g]).sum() * m["scale"] for j in js])
-            e = torch.exp(s)
-            pr = e / (1.0 + e.sum())
-            out[i, hd] = (pr[:, None] * torch.stack([v[j, g] for j in js])).sum(0) * gate[i, hd]
+    for i in range(T):
+        js = torch.tensor([j for j in range(T) if visible(i, j, m.get("mask"))])
+        for hd in range(H):
+            g = hd // (H // G)
+            e = torch.exp((k[js, g] @ q[i, hd]) * m["scale"])
+            pr = e / ((1.0 if sink else 0.0) + e.sum())
+            out[i, hd] = (pr[:, None] * v[js, g]).sum(0) * gate[i, hd]
     return out.reshape(T, H * vd) @ w[p + "o"].T, v_own
 
 
@@ -103,7 +102,7 @@ def feed_forward(mlp, w, p, h):
     return routed_ff(mlp, w, p, h)
 
 
-def forward(cfg, w, tokens: List[int], taps: Optional[list] = None, edit=None):
+def forward(cfg, w, tokens: List[int], taps: Optional[list] = None, edit=None, sink: bool = True):
     """Logits [T, vocab] of one sequence.  `taps`, a list, receives the residual stream after the embedding and after
     every layer.  `edit(cfg_layer_mixer)` may return a changed copy of a mixer's constants (tests use it to move a
     window's edge)."""
@@ -117,7 +116,7 @@ def forward(cfg, w, tokens: List[int], taps: Optional[list] = None, edit=None):
         h = dyt(x, w, p + "norm1")
         m = layer["mixer"] if edit is None else edit(dict(layer["mixer"]))
         wants = bool(m.get("v_mix"))
-        a, v_own = attention_mixer(m, eps, w, p + "mix.", h, v_first, wants and v_first is not None)
+        a, v_own = attention_mixer(m, eps, w, p + "mix.", h, v_first, wants and v_first is not None, sink)
         if wants and v_first is None:
             v_first = v_own
         x = x + (a + feed_forward(layer.get("mlp"), w, p + "mlp.", h))
