@@ -409,7 +409,69 @@ def vagonex_kernel_work(z, tokens, batch, ctx):
     }
 
 
-DESIGNS = {"satapel": lambda: (SATAPEL_SIZES, satapel_raw, gemma_raw_like, satapel_kernel_work, ("hos_wkv_scan",)),
+# ---- --design fobilorn: the Fobilorn design beside Gemma-2 at equal size ---------------------------------
+# A dense layer first, then layers of routed experts with a shared one; attention with a window that keeps the first
+# keys, values blended with the first layer's.  Gemma-2 "at equal size": the same width, layer count, vocabulary, heads,
+# head size, an intermediate size equal to what a Fobilorn token uses (top x ff + shared), the same window on its
+# windowed layers.
+FOBILORN_SIZES = {
+    "s": dict(width=1024, vocab=32000, layers=8, heads=8, kv_heads=2, dim=128, vdim=128, window=1024, keep=4,
+              dense_ff=4096, experts=8, top=2, ff=1024, shared=2048),
+    "m": dict(width=2048, vocab=32000, layers=8, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=4,
+              dense_ff=8192, experts=16, top=2, ff=1536, shared=3072),
+    "l": dict(width=4096, vocab=64000, layers=4, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=4,
+              dense_ff=14336, experts=32, top=4, ff=1024, shared=4096),
+}
+
+
+def fobilorn_raw(z):
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+             "mask": {"size": z["window"], "keep_first": z["keep"]}, "v_mix": True}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared"]}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["dense_ff"]}}] + \
+             [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(z["layers"] - 1)]
+    return {"architecture": "Fobilorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 10007}}, "layers": layers}
+
+
+def gemma_raw_like_fobilorn(z):
+    return dict(architectures=["Gemma2ForCausalLM"], model_type="gemma2", num_hidden_layers=z["layers"],
+                hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["dim"], intermediate_size=z["top"] * z["ff"] + z["shared"], vocab_size=z["vocab"],
+                rope_theta=10000.0, sliding_window=z["window"], max_position_embeddings=8192, query_pre_attn_scalar=z["dim"],
+                attn_logit_softcapping=50.0, final_logit_softcapping=30.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+
+
+def fobilorn_kernel_work(z, tokens, batch, ctx):
+    """Per launch of each of the design's own kernels: (bytes that must move, FLOPs of the mathematics) for a prompt of
+    `tokens` tokens and for a decode step of `batch` sequences at length `ctx` (bfloat16 cache and products, 32-bit rows)."""
+    H, G, kd, vd, W, K = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"], z["keep"]
+    seen = lambda p: min(p + 1, W) + min(K, max(0, p + 1 - W))        # keys position p sees
+    pairs = sum(seen(p) for p in range(tokens))
+    keys = seen(ctx - 1)
+    top, ff, width, E = z["top"], z["ff"], z["width"], z["experts"]
+    touched = min(E, batch * top)
+    attn = {"prefill": (tokens * G * (kd + vd) * 2 + tokens * H * (kd * 4 + vd * 2), 2.0 * pairs * H * (kd + vd)),
+            "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * H * (kd + vd))}
+    return {
+        "hos_gated_attn": attn, "hos_gated_attn_mma": attn, "hos_gated_attn_mma_decode": attn,
+        # the fused row in (32-bit), the other layer's values in, queries out (32-bit), keys and values out
+        "hos_qk_prep": {"prefill": (tokens * (H * kd * 8 + G * (kd * 6 + vd * 10)), 0.0),
+                        "decode": (batch * (H * kd * 8 + G * (kd * 6 + vd * 10)), 0.0)},
+        # x in and out (32-bit), two branch outputs in, the normed rows out
+        "hos_add_dyt": {"prefill": (tokens * width * 14, 0.0), "decode": (batch * width * 14, 0.0)},
+        "hos_moe_gate_up": {"prefill": (E * 2 * ff * width * 2, 4.0 * tokens * top * ff * width),
+                            "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * ff * width)},
+        "hos_moe_down": {"prefill": (E * ff * width * 2, 2.0 * tokens * top * ff * width),
+                         "decode": (touched * ff * width * 2, 2.0 * batch * top * ff * width)},
+        "hos_moe_combine": {"prefill": (tokens * width * (4 * top + 2 + 4), 0.0), "decode": (batch * width * (4 * top + 2 + 4), 0.0)},
+    }
+
+
+DESIGNS = {"fobilorn": lambda: (FOBILORN_SIZES, fobilorn_raw, gemma_raw_like_fobilorn, fobilorn_kernel_work,
+                                ("hos_gated_attn",)),
+           "satapel": lambda: (SATAPEL_SIZES, satapel_raw, gemma_raw_like, satapel_kernel_work, ("hos_wkv_scan",)),
            "vagonex": lambda: (VAGONEX_SIZES, vagonex_raw, gemma_raw_like_vagonex, vagonex_kernel_work,
                                ("hos_state_scan", "hos_gated_attn"))}
 
