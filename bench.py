@@ -12,7 +12,7 @@ back to the host, where the loop reads them one step late.  `prefill` is one pro
 step must read (every weight once, and the cache of the live sequences) to its time.
 `points` holds decoding at batch 1 and 64.  One JSON line is printed.
 
-`--design satapel` (or `vagonex`) is another measurement (not the line above): prompt and decode throughput of that design at
+`--design satapel` (or `vagonex`, `fobilorn`) is another measurement (not the line above): prompt and decode throughput of that design at
 a few sizes beside Gemma-2 at equal size, and each of the design's kernels against its roofline; one JSON line per size.
 With `--profile prefill|decode` it measures nothing and runs two such steps of one block of layers kernel by kernel, for a profiler.
 
@@ -486,6 +486,8 @@ def run_design_profile_step(args) -> int:
     from hos_b200.registry import config_from_dict
     sizes, raw_of, _, _, _ = DESIGNS[args.design]()
     z = dict(sizes[args.sizes.split(",")[0]], blocks=1)
+    if "layers" in z:
+        z["layers"] = min(4, z["layers"])
     b = int(args.batches.split(",")[-1])
     ctx = args.ctx if args.ctx != 8192 else 1024
     eng = Engine.from_config(config_from_dict(raw_of(z)), seed=0, dtype="bfloat16", max_batch=b,

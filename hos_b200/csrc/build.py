@@ -17,12 +17,16 @@ Libraries and what needs them:
               and for decoding over the paged cache
   gemm_tc     bfloat16 models: the tcgen05/TMA matrix product
   gemm_skinny bfloat16 models: the matrix product for up to 16 rows (decoding)
-  blocks      models built from the other kinds of block: the hashed token-pair embedding, the
-              parallel block's add-and-norms, attention over a latent cache, the matrix-state
-              recurrence, the routed feed-forward, the norm without statistics (Dynamic Tanh)
-  mixers      models with a norm after the residual sum, attention with a sink, chunks and a gate per
-              head over keys and values of unequal sizes, and the matrix-state recurrences with a
-              decay per head (constant, or per token with the delta rule and short convolutions)
+  rows        the hashed token-pair embedding, the parallel block's add-and-norms, the norm
+              without statistics (Dynamic Tanh)
+  experts     the routed feed-forward
+  blocks      attention over a latent cache, the matrix-state recurrence with its token shift
+  gated_attn  attention with a sink, chunks or a window (with kept first keys) and a gate per head
+              over keys and values of unequal sizes
+  mixers      a norm after the residual sum, the norm-and-gate of a mixer's heads, and the
+              matrix-state recurrences with a decay per head (constant, or per token with the
+              delta rule and short convolutions)
+A model builds only the libraries whose parts it has.
 """
 from __future__ import annotations
 
@@ -49,8 +53,11 @@ _STATIC_LIBS: Dict[str, Tuple[List[str], List[str]]] = {
     "core": (["elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu", "slot_state.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
-    "blocks": (["embed_pair.cu", "latent_attention.cu", "wkv.cu", "moe.cu", "dyt_norm.cu"], []),
-    "mixers": (["postnorm.cu", "gated_attention.cu", "gated_attention_mma.cu", "state_scan.cu"], []),
+    "rows": (["embed_pair.cu", "dyt_norm.cu"], []),
+    "experts": (["moe.cu"], []),
+    "blocks": (["latent_attention.cu", "wkv.cu"], []),
+    "gated_attn": (["gated_attention.cu", "gated_attention_mma.cu"], []),
+    "mixers": (["postnorm.cu", "state_scan.cu"], []),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -342,6 +342,8 @@ attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ 
 
 using namespace hos;
 
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
 // proj: float32 [N][ld], columns q (H * kd), then k (G * kd) and v (G * vd) if G > 0 (a call that reads another
 // call's cache passes G = 0 and projects neither), then whatever else the caller keeps there.  bias: the same
 // columns' biases or null.  q_norm / k_norm: [kd] or null (norm_whole: [H * kd] and [G * kd]).  freq: [rot_dims / 2] or

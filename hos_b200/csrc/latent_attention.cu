@@ -774,6 +774,8 @@ static int launch_attn(const float* q_lat, const void* kc, const void* k_pages, 
 
 using namespace hos;
 
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
 extern "C" int hos_latent_prep(const void* proj, int dtype, int proj_stride, int H, int dq, int R, int P,
                                const float* w_norm, float eps, const float* inv_freq, int rot_dims,
                                const int* token_pos, const int* token_seq, const int* seq_slot,

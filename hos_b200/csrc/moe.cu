@@ -24,50 +24,25 @@
 
 namespace hos {
 
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router,
-                                 const float* __restrict__ correction, const int* __restrict__ token_seq,
-                                 int* __restrict__ choice, float* __restrict__ weight, int D, int n_out, int top,
-                                 int scoring) {
-    pdl_enter();
-    extern __shared__ float z[];               // [n_out] scores, [n_out] taken flags, [warps][n_out] partial sums
-    float* taken = z + n_out;
-    const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+__device__ __forceinline__ float4 route_load4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 route_load4(const bf16* p) {
+    const uint2 u = *(const uint2*)p;
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xffff0000u));
+}
+
+// One warp: z [n_out] logits of row n (in shared memory) -> scores in place, the `top` largest of (score + correction)
+// and their plain scores.  A padding row (token_seq < 0) chooses nothing.
+__device__ __forceinline__ void route_choose(float* z, float* taken, const float* __restrict__ correction,
+                                             const int* __restrict__ token_seq, int* __restrict__ choice,
+                                             float* __restrict__ weight, int n, int n_out, int top, int scoring, int lane) {
     if (token_seq[n] < 0) {
-        for (int k = threadIdx.x; k < top; k += blockDim.x) {
+        for (int k = lane; k < top; k += 32) {
             choice[(size_t)n * top + k] = -1;
             weight[(size_t)n * top + k] = 0.f;
         }
         return;
     }
-    // every thread takes a slice of the row for all router outputs (all loads in flight at once), then the
-    // slices are added: per warp by shuffles, across warps through shared memory
-    const T* row = h + (size_t)n * D;
-    float* part = taken + n_out;               // [nwarps][n_out]
-    for (int e0 = 0; e0 < n_out; e0 += 8) {
-        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const int ne = min(8, n_out - e0);
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            const float x = to_float(row[d]);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (q < ne) s[q] = fmaf(x, router[(size_t)(e0 + q) * D + d], s[q]);
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const float v = warp_sum(s[q]);
-            if (lane == 0 && q < ne) part[warp * n_out + e0 + q] = v;
-        }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < n_out; e += blockDim.x) {
-        float v = 0.f;
-        for (int w = 0; w < nwarps; ++w) v += part[w * n_out + e];
-        z[e] = v;
-        taken[e] = 0.f;
-    }
-    __syncthreads();
-    if (warp != 0) return;
     if (scoring == 1) {
         for (int e = lane; e < n_out; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
     } else {
@@ -112,6 +87,116 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         }
         __syncwarp();
     }
+}
+
+// A block takes RT rows, so that the 32-bit router matrix is read once for all of them.  Every thread takes a slice of
+// the columns (four neighbouring ones at a time where the width allows) for eight router outputs at a time and all RT
+// rows; the slices are added per warp by shuffles and across the warps through shared memory, in the same order
+// whatever RT is: a row's logits do not depend on its neighbours in the block.  Then a warp per row scores and chooses.
+template <typename T, int RT, bool VEC>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
+                 const int* __restrict__ token_seq, int* __restrict__ choice, float* __restrict__ weight, int N, int D,
+                 int n_out, int top, int scoring, float* __restrict__ logits) {
+    pdl_enter();
+    extern __shared__ float route_sm[];
+    float* z_all = route_sm;                       // [RT][n_out] scores
+    float* taken_all = z_all + RT * n_out;         // [RT][n_out] flags
+    float* part = taken_all + RT * n_out;          // [warps][RT][n_out] partial sums
+    const int n0 = blockIdx.x * RT, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const T* rows[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) rows[r] = h + (size_t)min(n0 + r, N - 1) * D;     // rows beyond the last: computed, not written
+    // with `logits` the grid's second dimension cuts the router outputs into groups of eight: a block leaves its
+    // group's logits there and moe_choose_kernel scores and chooses; without, one block does all of it
+    const int e_lo = logits != nullptr ? blockIdx.y * 8 : 0, e_hi = logits != nullptr ? min(n_out, e_lo + 8) : n_out;
+    for (int e0 = e_lo; e0 < e_hi; e0 += 8) {
+        float s[RT][8];
+#pragma unroll
+        for (int r = 0; r < RT; ++r)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) s[r][q] = 0.f;
+        const int ne = min(8, n_out - e0);
+        if constexpr (VEC) {
+            for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+                float4 x[RT];
+#pragma unroll
+                for (int r = 0; r < RT; ++r) x[r] = route_load4(rows[r] + d);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (q < ne) {
+                        const float4 w = *(const float4*)(router + (size_t)(e0 + q) * D + d);
+#pragma unroll
+                        for (int r = 0; r < RT; ++r)
+                            s[r][q] = fmaf(x[r].w, w.w, fmaf(x[r].z, w.z, fmaf(x[r].y, w.y, fmaf(x[r].x, w.x, s[r][q]))));
+                    }
+                }
+            }
+        } else {
+            for (int d = threadIdx.x; d < D; d += blockDim.x) {
+                float x[RT];
+#pragma unroll
+                for (int r = 0; r < RT; ++r) x[r] = to_float(rows[r][d]);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (q < ne) {
+                        const float w = router[(size_t)(e0 + q) * D + d];
+#pragma unroll
+                        for (int r = 0; r < RT; ++r) s[r][q] = fmaf(x[r], w, s[r][q]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RT; ++r)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float v = warp_sum(s[r][q]);
+                if (lane == 0 && q < ne) part[(warp * RT + r) * n_out + e0 + q] = v;
+            }
+    }
+    __syncthreads();
+    if (logits != nullptr) {
+        for (int i = threadIdx.x; i < RT * 8; i += blockDim.x) {
+            const int r = i >> 3, e = e_lo + (i & 7);
+            if (e >= e_hi || n0 + r >= N) continue;
+            float v = 0.f;
+            for (int w = 0; w < nwarps; ++w) v += part[(w * RT + r) * n_out + e];
+            logits[(size_t)(n0 + r) * n_out + e] = v;
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < RT * n_out; i += blockDim.x) {
+        float v = 0.f;
+        for (int w = 0; w < nwarps; ++w) v += part[w * RT * n_out + i];
+        z_all[i] = v;
+        taken_all[i] = 0.f;
+    }
+    __syncthreads();
+    if (warp >= RT) return;
+    const int n = n0 + warp;
+    if (n >= N) return;
+    route_choose(z_all + warp * n_out, taken_all + warp * n_out, correction, token_seq, choice, weight, n, n_out, top, scoring,
+                 lane);
+}
+
+// A warp per row: logits [N][n_out] from moe_route_kernel's blocks -> scores, the `top` largest, their weights.
+__global__ void __launch_bounds__(128)
+moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ correction, const int* __restrict__ token_seq,
+                  int* __restrict__ choice, float* __restrict__ weight, int N, int n_out, int top, int scoring) {
+    pdl_enter();
+    extern __shared__ float route_sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int n = blockIdx.x * nwarps + warp;
+    if (n >= N) return;
+    float* z = route_sm + (size_t)warp * 2 * n_out;
+    float* taken = z + n_out;
+    for (int e = lane; e < n_out; e += 32) {
+        z[e] = logits[(size_t)n * n_out + e];
+        taken[e] = 0.f;
+    }
+    __syncwarp();
+    route_choose(z, taken, correction, token_seq, choice, weight, n, n_out, top, scoring, lane);
 }
 
 // One block.  listed: [cap] pair ids (row * top + choice) expert by expert, -1 where a tile is padded;
@@ -492,23 +577,53 @@ __global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int
 
 using namespace hos;
 
+extern "C" const char* hos_last_error() { return error_buffer(); }
+
 extern "C" int hos_moe_tile_rows() { return kTile; }
 
 extern "C" int hos_moe_route(const void* h, int dtype, const float* router, const float* correction,
                              const int* token_seq, int* choice, float* weight, int N, int D, int n_out, int top,
-                             int scoring, cudaStream_t stream) {
+                             int scoring, float* logits, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (top <= 0 || top > n_out) HOS_REFUSE("moe_route: %d of %d router outputs cannot be chosen", top, n_out);
-    const size_t smem = (size_t)(2 + 8) * n_out * sizeof(float);       // scores, flags, and a partial sum per warp (8 warps)
+    // rows to a block: as many as pay (the router matrix is read once per block) and as shared memory holds
+    int rt = N >= 1024 ? 8 : N >= 16 ? 4 : 1;
+    auto smem_of = [&](int r) { return (size_t)(2 + 8) * r * n_out * sizeof(float); };   // scores, flags, a partial sum per warp
+    while (rt > 1 && smem_of(rt) > 48 * 1024) rt = rt == 8 ? 4 : 1;
+    const size_t smem = smem_of(rt);
     if (smem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
-    if (dtype == kBF16)
-        launch_pdl(moe_route_kernel<bf16>, dim3(N), dim3(256), smem, stream, (const bf16*)h, router, correction, token_seq,
-                   choice, weight, D, n_out, top, scoring);
-    else if (dtype == kF32)
-        launch_pdl(moe_route_kernel<float>, dim3(N), dim3(256), smem, stream, (const float*)h, router, correction, token_seq,
-                   choice, weight, D, n_out, top, scoring);
-    else
-        HOS_REFUSE("moe_route: unknown dtype %d", dtype);
+    if (dtype != kBF16 && dtype != kF32) HOS_REFUSE("moe_route: unknown dtype %d", dtype);
+    const bool vec = D % 4 == 0 && (uintptr_t)router % 16 == 0 && (uintptr_t)h % (dtype == kBF16 ? 8 : 16) == 0;
+    const unsigned blocks = (unsigned)((N + rt - 1) / rt);
+    // few blocks and more than eight outputs: the outputs' groups of eight go to blocks of their own (grid.y) and a
+    // second launch chooses; the caller then gives `logits` [N][n_out]
+    if (blocks >= 296u || n_out <= 8) logits = nullptr;
+    const unsigned groups = logits != nullptr ? (unsigned)((n_out + 7) / 8) : 1u;
+#define HOS_ROUTE(T, RT, VEC)                                                                                        \
+    launch_pdl(moe_route_kernel<T, RT, VEC>, dim3(blocks, groups), dim3(256), smem, stream, (const T*)h, router,     \
+               correction, token_seq, choice, weight, N, D, n_out, top, scoring, logits)
+#define HOS_ROUTE_V(T, RT)                                                                                           \
+    do {                                                                                                             \
+        if (vec) HOS_ROUTE(T, RT, true);                                                                             \
+        else HOS_ROUTE(T, RT, false);                                                                                \
+    } while (0)
+#define HOS_ROUTE_R(T)                                                                                               \
+    do {                                                                                                             \
+        if (rt == 8) HOS_ROUTE_V(T, 8);                                                                              \
+        else if (rt == 4) HOS_ROUTE_V(T, 4);                                                                         \
+        else HOS_ROUTE_V(T, 1);                                                                                      \
+    } while (0)
+    if (dtype == kBF16) HOS_ROUTE_R(bf16);
+    else HOS_ROUTE_R(float);
+#undef HOS_ROUTE_R
+#undef HOS_ROUTE_V
+#undef HOS_ROUTE
+    if (logits != nullptr) {
+        const size_t csmem = (size_t)4 * 2 * n_out * sizeof(float);
+        if (csmem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
+        launch_pdl(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), csmem, stream, (const float*)logits, correction, token_seq,
+                   choice, weight, N, n_out, top, scoring);
+    }
     return check_launch("moe_route");
 }
 

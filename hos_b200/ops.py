@@ -531,10 +531,40 @@ _blocks: Optional[Library] = None
 
 
 def blocks() -> Library:
+    """Attention over a latent cache and the matrix-state recurrence with its token shift."""
     global _blocks
     if _blocks is None:
         _blocks = Library("blocks")
     return _blocks
+
+
+_rows_lib: Optional[Library] = None
+_experts: Optional[Library] = None
+_gated_attn_lib: Optional[Library] = None
+
+
+def rows_lib() -> Library:
+    """The hashed token-pair embedding, the parallel block's add-and-norms, the norm without statistics."""
+    global _rows_lib
+    if _rows_lib is None:
+        _rows_lib = Library("rows")
+    return _rows_lib
+
+
+def experts() -> Library:
+    """The routed feed-forward."""
+    global _experts
+    if _experts is None:
+        _experts = Library("experts")
+    return _experts
+
+
+def gated_attn_lib() -> Library:
+    """Attention with a gate per head, a sink, chunks or a window, keys and values of unequal sizes."""
+    global _gated_attn_lib
+    if _gated_attn_lib is None:
+        _gated_attn_lib = Library("gated_attn")
+    return _gated_attn_lib
 
 
 def embed_pair(step, prev_token: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, buckets: int,
@@ -547,13 +577,13 @@ def embed_pair(step, prev_token: torch.Tensor, table: torch.Tensor, pair_table: 
     n, d = out.shape
     if table.dtype != pair_table.dtype or table.shape[1] != d or pair_table.shape != (buckets + 1, d):
         raise KernelError("embed_pair: the tables do not fit each other or the output")
-    blocks().call("hos_embed_pair", _ptr(step.tokens), _ptr(step.token_pos), _ptr(step.token_seq),
+    rows_lib().call("hos_embed_pair", _ptr(step.tokens), _ptr(step.token_pos), _ptr(step.token_seq),
                   _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(prev_token), _ptr(table), _ptr(pair_table),
                   dtype_code(table.dtype), int(buckets), int(mul_prev), int(mul_cur), _ptr(out), n, d, _stream())
 
 
 def keep_last_token(step, prev_token: torch.Tensor) -> None:
-    blocks().call("hos_keep_last_token", _ptr(step.tokens), _ptr(step.token_seq), _ptr(step.cu_seqlens),
+    rows_lib().call("hos_keep_last_token", _ptr(step.tokens), _ptr(step.token_seq), _ptr(step.cu_seqlens),
                   _ptr(step.seq_slot), _ptr(prev_token), int(step.n_seqs), _stream())
 
 
@@ -572,7 +602,7 @@ def scaled_add_norms(a: Optional[torch.Tensor], f: Optional[torch.Tensor], mult:
     if h1 is not None and h2 is not None and h1.dtype != h2.dtype:
         raise KernelError("scaled_add_norms: the two norm outputs differ in dtype")
     h = h1 if h1 is not None else h2
-    blocks().call("hos_scaled_add_norms", _ptr(a), dtype_code(a.dtype) if a is not None else 0,
+    rows_lib().call("hos_scaled_add_norms", _ptr(a), dtype_code(a.dtype) if a is not None else 0,
                   _ptr(f), dtype_code(f.dtype) if f is not None else 0, float(mult), _ptr(x),
                   _ptr(w1), float(eps1), _ptr(h1), _ptr(w2), float(eps2), _ptr(h2),
                   dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
@@ -674,7 +704,7 @@ _moe_tile: Optional[int] = None
 def moe_tile_rows() -> int:
     global _moe_tile
     if _moe_tile is None:
-        f = blocks().lib.hos_moe_tile_rows
+        f = experts().lib.hos_moe_tile_rows
         f.restype, f.argtypes = ctypes.c_int, []
         _moe_tile = int(f())
     return _moe_tile
@@ -687,12 +717,14 @@ def moe_route(h, router, correction, token_seq, choice, weight, top: int, scorin
     _check(h, "rows", None, 2)
     _check(router, "router", torch.float32, 2)
     n, d = h.shape
-    blocks().call("hos_moe_route", _ptr(h), dtype_code(h.dtype), _ptr(router), _ptr(correction), _ptr(token_seq),
-                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), int(scoring), _stream())
+    # few rows and many router outputs: the outputs are cut over blocks, which leave their logits here for a second launch
+    logits = torch.empty((n, router.shape[0]), dtype=torch.float32, device=h.device) if router.shape[0] > 8 and n < 2048 else None
+    experts().call("hos_moe_route", _ptr(h), dtype_code(h.dtype), _ptr(router), _ptr(correction), _ptr(token_seq),
+                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), int(scoring), _ptr(logits), _stream())
 
 
 def moe_align(choice, n_experts: int, listed, tile_expert) -> None:
-    blocks().call("hos_moe_align", _ptr(choice), choice.numel(), int(n_experts), _ptr(listed), listed.numel(),
+    experts().call("hos_moe_align", _ptr(choice), choice.numel(), int(n_experts), _ptr(listed), listed.numel(),
                   _ptr(tile_expert), tile_expert.numel(), _stream())
 
 
@@ -700,14 +732,14 @@ def moe_gate_up(h, w, listed, tile_expert, y, top: int, limit: float, alpha: flo
                 in_weight: Optional[torch.Tensor] = None) -> None:
     """in_weight ([pairs] float32): the pair's weight multiplies the expert's input (then `moe_down` takes none)."""
     _check(w, "expert gate/up weights", h.dtype, 3)
-    blocks().call("hos_moe_gate_up", _ptr(h), _ptr(w), dtype_code(h.dtype), _ptr(listed), _ptr(tile_expert), _ptr(y),
+    experts().call("hos_moe_gate_up", _ptr(h), _ptr(w), dtype_code(h.dtype), _ptr(listed), _ptr(tile_expert), _ptr(y),
                   tile_expert.numel(), h.shape[1], w.shape[1] // 2, int(top), float(limit), float(alpha), float(up_shift),
                   _ptr(in_weight), _stream())
 
 
 def moe_down(y, w, listed, tile_expert, weight, pair_out) -> None:
     _check(w, "expert down weights", y.dtype, 3)
-    blocks().call("hos_moe_down", _ptr(y), _ptr(w), dtype_code(y.dtype), _ptr(listed), _ptr(tile_expert), _ptr(weight),
+    experts().call("hos_moe_down", _ptr(y), _ptr(w), dtype_code(y.dtype), _ptr(listed), _ptr(tile_expert), _ptr(weight),
                   _ptr(pair_out), tile_expert.numel(), w.shape[1], w.shape[2], _stream())
 
 
@@ -715,7 +747,7 @@ def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_exper
             up_shift: float = 1.0, weight_on_input: bool = False) -> bool:
     """Both expert products for a handful of (row, choice) pairs, without lists or tiles (decoding at small batch):
     y [pairs, F] and pair_out [pairs, D] by pair id.  False: the sizes are not these kernels' and nothing ran."""
-    lib = blocks()
+    lib = experts()
     global launch_count
     pairs, d, f = choice.numel(), h.shape[1], w_down.shape[2]
     rc = lib.fn("hos_moe_gate_up_few")(_ptr(h), _ptr(w_gate_up), _ptr(choice), _ptr(y), pairs, d, f, int(top), int(n_experts),
@@ -741,7 +773,7 @@ def moe_combine(pair_out, choice, weight, h, out, top: int, n_experts: int, extr
         _check(extra, "the shared expert's output", h.dtype, 2)
         if extra.shape != h.shape:
             raise KernelError("moe_combine: the shared expert's output and the rows differ in size")
-    blocks().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),
+    experts().call("hos_moe_combine", _ptr(pair_out), _ptr(choice), _ptr(weight), _ptr(h), dtype_code(h.dtype), _ptr(out),
                   n, d, int(top), int(n_experts), _ptr(extra), _stream())
 
 
@@ -766,7 +798,7 @@ def add_dyt(a: Optional[torch.Tensor], f: Optional[torch.Tensor], mult: float, x
         _check(b, "norm bias", torch.float32, 1)
         if h.shape != x.shape or w.shape[0] != d or b.shape[0] != d:
             raise KernelError("add_dyt: sizes of the norm disagree")
-    blocks().call("hos_add_dyt", _ptr(a), dtype_code(a.dtype) if a is not None else 0, parts[0],
+    rows_lib().call("hos_add_dyt", _ptr(a), dtype_code(a.dtype) if a is not None else 0, parts[0],
                   _ptr(f), dtype_code(f.dtype) if f is not None else 0, parts[1], float(mult), _ptr(x), float(alpha),
                   _ptr(w), _ptr(b), _ptr(h), dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
 
@@ -852,7 +884,7 @@ def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[t
         if v_first.shape[0] != n or v_first_col + n_kv * vd > v_first.shape[1]:
             raise KernelError("qk_prep: the other layer's values do not fit this layer's")
         vf_ptr, vf_ld = ctypes.c_void_p(v_first.data_ptr() + 4 * v_first_col), v_first.shape[1]
-    mixers().call("hos_qk_prep", _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freq),
+    gated_attn_lib().call("hos_qk_prep", _ptr(proj), proj.shape[1], _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freq),
                   int(rot_dims), float(magnitude), _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
                   _ptr(q_out), _ptr(cache.k_pages) if n_kv else None, _ptr(cache.v_pages) if n_kv else None,
                   dtype_code(cache.k_pages.dtype), _ptr(cache.page_table), cache.table_stride, cache.ring_pages, n,
@@ -873,7 +905,7 @@ def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor]
     if n_splits > 1:
         part_acc = torch.empty((n, heads, n_splits, vd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q.device)
-    mixers().call("hos_gated_attn", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), dtype_code(cache.k_pages.dtype),
+    gated_attn_lib().call("hos_gated_attn", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), dtype_code(cache.k_pages.dtype),
                   _ptr(cache.page_table), cache.table_stride, cache.ring_pages, _ptr(sink),
                   ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
                   gate.shape[1] if gate is not None else 0, _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
@@ -892,7 +924,7 @@ def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Ten
         return False
     if kd not in (64, 128) or vd not in (64, 128) or q.data_ptr() % 16 or out.data_ptr() % 4:
         return False
-    mixers().call("hos_gated_attn_mma", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
+    gated_attn_lib().call("hos_gated_attn_mma", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
                   cache.table_stride, cache.ring_pages, _ptr(sink),
                   ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
                   gate.shape[1] if gate is not None else 0, _ptr(step.cu_seqlens), _ptr(step.token_pos),
@@ -918,13 +950,13 @@ def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[to
         part_ml = torch.empty((n, heads, n_splits, 2), dtype=torch.float32, device=q.device)
     gate_ptr = ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None
     gate_ld = gate.shape[1] if gate is not None else 0
-    mixers().call("hos_gated_attn_mma_decode", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
+    gated_attn_lib().call("hos_gated_attn_mma_decode", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
                   cache.table_stride, cache.ring_pages, _ptr(sink), gate_ptr, gate_ld, _ptr(step.token_pos),
                   _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), _ptr(part_acc), _ptr(part_ml), int(n_splits), n,
                   heads, cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0),
                   _stream())
     if n_splits > 1:
-        mixers().call("hos_attn_merge", _ptr(part_acc), _ptr(part_ml), int(n_splits), gate_ptr, gate_ld,
+        gated_attn_lib().call("hos_attn_merge", _ptr(part_acc), _ptr(part_ml), int(n_splits), gate_ptr, gate_ld,
                       _ptr(step.token_seq), _ptr(out), dtype_code(out.dtype), n, heads, vd, _stream())
     return True
 

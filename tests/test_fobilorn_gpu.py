@@ -566,3 +566,42 @@ def test_the_attention_kernels_alone_against_float64():
                 assert ops.gated_attn_mma_decode(q1, cache, sink, g1, ld - H, step1, out1, scale, 0, window, shares, keep)
                 err = float((out1.double().cpu().view(3, H, vd) - want[last]).abs().max())
                 assert err < tol * max(1.0, float(want.abs().max())), f"single tokens, {kd}/{vd}, {shares} shares: {err:.2e}"
+
+
+def test_the_router_kernel_alone_against_float64():
+    """Logistic scores of 32-bit logits, the `top` largest, the plain scores as weights: few rows and many (a block
+    takes one, four or eight rows), few outputs and many (their groups of eight on blocks of their own), widths that are
+    and are not multiples of four, 32-bit and bfloat16 rows, padding rows.  A row's logits do not depend on how many
+    rows come with it: the weights of a row alone and in a batch are the same numbers."""
+    from hos_b200 import ops
+    dev = "cuda"
+    torch.manual_seed(9)
+    for n, d, n_out, top in ((1, 100, 3, 1), (5, 64, 8, 8), (17, 1024, 40, 6), (70, 250, 9, 2), (1100, 128, 16, 3),
+                             (2100, 96, 33, 4), (16, 4096, 300, 5)):
+        router = torch.randn(n_out, d, device=dev) * (3.0 / d ** 0.5)
+        for dtype in (torch.float32, torch.bfloat16):
+            h = torch.randn(n, d, device=dev).to(dtype)
+            seq = torch.zeros(n, dtype=torch.int32, device=dev)
+            if n > 2:
+                seq[n // 2] = -1                                         # a padding row
+            choice = torch.full((n * top,), -7, dtype=torch.int32, device=dev)
+            weight = torch.full((n * top,), -7.0, device=dev)
+            ops.moe_route(h, router, None, seq, choice, weight, top, ops.MOE_SCORING["logistic"])
+            s64 = torch.sigmoid(h.double().cpu() @ router.double().cpu().T)
+            choice, weight = choice.cpu().view(n, top), weight.cpu().view(n, top)
+            for r in range(n):
+                if n > 2 and r == n // 2:
+                    assert choice[r].tolist() == [-1] * top and weight[r].tolist() == [0.0] * top
+                    continue
+                order = sorted(range(n_out), key=lambda e: (-float(s64[r, e]), e))
+                got = choice[r].tolist()
+                assert len(set(got)) == top and all(0 <= e < n_out for e in got)
+                # the chosen ones are the largest (a tie within 32-bit rounding may come in either order)
+                assert float(s64[r, got].min()) >= float(s64[r, order[top - 1]]) - 1e-6, (n, d, n_out, r)
+                assert float((weight[r].double() - s64[r, got]).abs().max()) < 1e-5
+                assert all(float(weight[r, k]) >= float(weight[r, k + 1]) for k in range(top - 1))
+            if n > 1:
+                c1 = torch.empty(top, dtype=torch.int32, device=dev)
+                w1 = torch.empty(top, device=dev)
+                ops.moe_route(h[n - 1:].clone(), router, None, seq[:1], c1, w1, top, ops.MOE_SCORING["logistic"])
+                assert torch.equal(c1.cpu(), choice[n - 1]) and torch.equal(w1.cpu(), weight[n - 1]), "alone and in a batch differ"
