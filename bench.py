@@ -615,7 +615,7 @@ def main() -> int:
                     help="the sequences end at 1, 1/2, 1/4, 1/8, 1/16, 1/16, 1/32, 1/32 of the context, in turn, "
                          "instead of all at its end (not the driver's line: how a batch of unequal lengths decodes)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
-                    help="length of the timed prompt (default: the contract's 2,048)")
+                    help="length of the timed prompt (default: 2,048)")
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="not the driver's line: prompt and decode throughput of this design beside Gemma-2 at equal "
                          "size, with its kernels against their rooflines (--sizes, --batches, --ctx, --prefill-tokens)")
