@@ -36,8 +36,8 @@ __device__ __forceinline__ int table_entry(const PagedKV2& c, int lp) { return c
 
 constexpr int kPrepMaxPL = 16;    // a head of up to 32 * 16 numbers in a warp's registers
 
-template <typename TC, int kPrepPL>
-__global__ void __launch_bounds__(128)
+template <typename TC, int kPrepPL, int kThreads>
+__global__ void __launch_bounds__(kThreads)
 qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias, const float* __restrict__ q_norm,
                const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims, float magnitude,
                const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
@@ -71,7 +71,7 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
         }
     }
     // query heads 0..H-1, then key heads H..H+G-1
-    for (int item = warp; item < H + G; item += 4) {
+    for (int item = warp; item < H + G; item += kThreads / 32) {
         const bool is_q = item < H;
         const int col0 = item * kd;                      // q heads and k heads follow one another in the row
         const float* nw = is_q ? q_norm : k_norm;
@@ -308,7 +308,8 @@ gated_attn_kernel(const float* __restrict__ q, PagedKV2 cache, const float* __re
     }
 }
 
-// one warp per (token, head): the shares' sums under one maximum
+// one warp per (token, head): the shares' sums under one maximum.  The lanes first take a share each (maximum and
+// sum), then 128 value columns at a time, four to a lane, with the shares' rows as independent loads.
 __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_splits,
                   const float* __restrict__ gate, long long gate_stride, const int* __restrict__ token_seq,
@@ -319,22 +320,41 @@ attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ 
     if (item >= (long long)n_tokens * H) return;
     const int n = (int)(item / H), h = (int)(item % H);
     const float* ml = part_ml + (size_t)item * n_splits * 2;
-    float m = -INFINITY;
     const bool live = token_seq[n] >= 0;
+    float m = -INFINITY;
     if (live)
-        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+        for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
+    m = warp_max(m);
     float l = 0.f;
     if (live)
-        for (int s = 0; s < n_splits; ++s) l += ml[2 * s + 1] > 0.f ? ml[2 * s + 1] * expf(ml[2 * s] - m) : 0.f;
+        for (int s = lane; s < n_splits; s += 32) l += ml[2 * s + 1] > 0.f ? ml[2 * s + 1] * expf(ml[2 * s] - m) : 0.f;
+    l = warp_sum(l);
     float f = l > 0.f ? 1.f / l : 0.f;
     if (live && gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h]));
-    for (int d = lane; d < vd; d += 32) {
-        float a = 0.f;
-        if (live)
-            for (int s = 0; s < n_splits; ++s)
-                if (ml[2 * s + 1] > 0.f) a = fmaf(part_acc[((size_t)item * n_splits + s) * vd + d], expf(ml[2 * s] - m), a);
-        if (out_bf16) ((bf16*)out)[(size_t)item * vd + d] = from_float<bf16>(a * f);
-        else ((float*)out)[(size_t)item * vd + d] = a * f;
+    const float* acc_rows = part_acc + (size_t)item * n_splits * vd;
+    for (int d0 = 0; d0 < vd; d0 += 128) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+#pragma unroll 4
+            for (int s = 0; s < n_splits; ++s) {
+                const float w = ml[2 * s + 1] > 0.f ? expf(ml[2 * s] - m) : 0.f;     // a share without keys: its row does not count
+                float x[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int d = d0 + lane + 32 * i;
+                    x[i] = d < vd ? acc_rows[(size_t)s * vd + d] : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = w > 0.f ? fmaf(x[i], w, a[i]) : a[i];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = d0 + lane + 32 * i;
+            if (d >= vd) continue;
+            if (out_bf16) ((bf16*)out)[(size_t)item * vd + d] = from_float<bf16>(a[i] * f);
+            else ((float*)out)[(size_t)item * vd + d] = a[i] * f;
+        }
     }
 }
 
@@ -358,9 +378,17 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
     if (freq == nullptr) rot_dims = 0;
     if (rot_dims % 2 != 0 || rot_dims > kd) HOS_REFUSE("qk_prep: %d rotated numbers in heads of %d", rot_dims, kd);
     PagedKV2 c{k_pages, v_pages, page_table, table_stride, ring_pages, G, kd, vd};
+    // few rows (single-token steps): a block of 16 warps shortens the row's chain of loads; many rows: 4 warps
+    const bool wide = N <= 592 && H + G > 4;
+#define HOS_QKP_N(TC, PL, NT)                                                                                        \
+    launch_pdl(qk_prep_kernel<TC, PL, NT>, dim3(N), dim3(NT), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq,   \
+               rot_dims, magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd, norm_whole, v_first,     \
+               v_first_ld, v_mix)
 #define HOS_QKP(TC, PL)                                                                                              \
-    launch_pdl(qk_prep_kernel<TC, PL>, dim3(N), dim3(128), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq, rot_dims, \
-               magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd, norm_whole, v_first, v_first_ld, v_mix)
+    do {                                                                                                             \
+        if (wide) HOS_QKP_N(TC, PL, 512);                                                                            \
+        else HOS_QKP_N(TC, PL, 128);                                                                                 \
+    } while (0)
 #define HOS_QKP_T(TC)                                                                                                \
     do {                                                                                                             \
         if (kd <= 32) HOS_QKP(TC, 1);                                                                                \
@@ -373,6 +401,7 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
     else HOS_QKP_T(float);
 #undef HOS_QKP_T
 #undef HOS_QKP
+#undef HOS_QKP_N
     return check_launch("qk_prep");
 }
 

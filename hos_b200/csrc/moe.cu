@@ -555,22 +555,40 @@ moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, cons
     }
 }
 
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice,
-                                   const float* __restrict__ weight, const T* __restrict__ h, float* __restrict__ out,
-                                   int D, int top, int n_experts, const T* __restrict__ extra) {
+// A block per row and per 256 * VEC columns: the chosen pairs' rows are independent loads, so a row of any width
+// costs one round of them.  VEC = 4 where the width and the addresses allow 16-byte accesses.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ choice, const float* __restrict__ weight,
+                   const T* __restrict__ h, float* __restrict__ out, int D, int top, int n_experts,
+                   const T* __restrict__ extra) {
     pdl_enter();
     const int n = blockIdx.x;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float s = extra ? to_float(extra[(size_t)n * D + d]) : 0.f;
-        for (int k = 0; k < top; ++k) {
-            const size_t id = (size_t)n * top + k;
-            const int e = choice[id];
-            if (e < 0) continue;
-            s += e < n_experts ? pair_out[id * D + d] : weight[id] * to_float(h[(size_t)n * D + d]);
+    const int d = (blockIdx.y * 256 + threadIdx.x) * VEC;
+    if (d >= D) return;
+    float s[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s[i] = extra ? to_float(extra[(size_t)n * D + d + i]) : 0.f;
+#pragma unroll 4
+    for (int k = 0; k < top; ++k) {
+        const size_t id = (size_t)n * top + k;
+        const int e = choice[id];
+        if (e < 0) continue;
+        if (e < n_experts) {
+            if constexpr (VEC == 4) {
+                const float4 p = *(const float4*)(pair_out + id * D + d);
+                s[0] += p.x; s[1] += p.y; s[2] += p.z; s[3] += p.w;
+            } else {
+                s[0] += pair_out[id * D + d];
+            }
+        } else {
+            const float w = weight[id];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) s[i] = fmaf(w, to_float(h[(size_t)n * D + d + i]), s[i]);
         }
-        out[(size_t)n * D + d] = s;
     }
+    if constexpr (VEC == 4) *(float4*)(out + (size_t)n * D + d) = make_float4(s[0], s[1], s[2], s[3]);
+    else out[(size_t)n * D + d] = s[0];
 }
 
 }  // namespace hos
@@ -689,14 +707,21 @@ extern "C" int hos_moe_down(const void* y, const void* W, int dtype, const int* 
 extern "C" int hos_moe_combine(const float* pair_out, const int* choice, const float* weight, const void* h, int dtype,
                                float* out, int N, int D, int top, int n_experts, const void* extra, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (dtype == kBF16)
-        launch_pdl(moe_combine_kernel<bf16>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const bf16*)h, out, D,
-                   top, n_experts, (const bf16*)extra);
-    else if (dtype == kF32)
-        launch_pdl(moe_combine_kernel<float>, dim3(N), dim3(256), 0, stream, pair_out, choice, weight, (const float*)h, out,
-                   D, top, n_experts, (const float*)extra);
-    else
+    const bool vec = D % 4 == 0 && ((uintptr_t)pair_out | (uintptr_t)out) % 16 == 0;
+    const dim3 grid((unsigned)N, (unsigned)((D + (vec ? 1024 : 256) - 1) / (vec ? 1024 : 256)));
+    if (grid.y > 65535) HOS_REFUSE("moe_combine: rows of %d numbers are more than one launch takes", D);
+#define HOS_COMBINE(T, VEC)                                                                                          \
+    launch_pdl(moe_combine_kernel<T, VEC>, grid, dim3(256), 0, stream, pair_out, choice, weight, (const T*)h, out, D, top, \
+               n_experts, (const T*)extra)
+    if (dtype == kBF16) {
+        if (vec) HOS_COMBINE(bf16, 4);
+        else HOS_COMBINE(bf16, 1);
+    } else if (dtype == kF32) {
+        if (vec) HOS_COMBINE(float, 4);
+        else HOS_COMBINE(float, 1);
+    } else
         HOS_REFUSE("moe_combine: unknown dtype %d", dtype);
+#undef HOS_COMBINE
     return check_launch("moe_combine");
 }
 
