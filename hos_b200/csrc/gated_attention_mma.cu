@@ -62,6 +62,18 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
     auto tile_of = [&](int it) { return it < n_keep ? it : kt_lo + it - n_keep; };
     const int* table = page_table + (size_t)seq_slot[seq] * table_stride;
 
+    auto load_kv = [&](int kt, int stage) {
+        const int lp = kt;                                          // a tile is a page
+        const int page = table[ring_pages > 0 ? lp % ring_pages : lp];
+        const bf16* ksrc = k_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * KD;
+        const bf16* vsrc = v_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * VD;
+        bf16* ks = kv_s + (size_t)stage * kStage;
+        bf16* vs = ks + MK * KD;
+        for (int i = threadIdx.x; i < MK * (KD / 8); i += 128) cp16(ks + i * 8, ksrc + i * 8);
+        for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
+    };
+    load_kv(tile_of(0), 0);                                         // under way while the queries are staged
+    cp_commit();
     // the queries: 32-bit rows, rounded here to the tensor cores' type; rows beyond the sequence are zeros
     for (int i = threadIdx.x; i < MQ * (KD / 8); i += 128) {
         const int r = i / (KD / 8), c = i % (KD / 8);
@@ -73,18 +85,6 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
         }
         *reinterpret_cast<uint4*>(q_s + tile_chunk_offset<KD>(r, c)) = packed;
     }
-    auto load_kv = [&](int kt, int stage) {
-        const int lp = kt;                                          // a tile is a page
-        const int page = table[ring_pages > 0 ? lp % ring_pages : lp];
-        const bf16* ksrc = k_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * KD;
-        const bf16* vsrc = v_pages + ((size_t)page * G + kvh) * (size_t)kPageTokens * VD;
-        bf16* ks = kv_s + (size_t)stage * kStage;
-        bf16* vs = ks + MK * KD;
-        for (int i = threadIdx.x; i < MK * (KD / 8); i += 128) cp16(ks + i * 8, ksrc + i * 8);
-        for (int i = threadIdx.x; i < MK * (VD / 8); i += 128) cp16(vs + i * 8, vsrc + i * 8);
-    };
-    load_kv(tile_of(0), 0);
-    cp_commit();
 
     const float sk = sink != nullptr ? sink[head] : -INFINITY;
     float m_run[2] = {sk, sk};
@@ -99,6 +99,13 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
     for (int r = 0; r < 2; ++r) {
         qlo[r] = chunk > 0 ? qpos[r] / chunk * chunk : 0;
         if (window > 0) qlo[r] = max(qlo[r], qpos[r] + 1 - window);
+    }
+    // the largest first key among the warp's 16 queries (its last one's)
+    int qlo_max;
+    {
+        const int q_last = p0 + warp * 16 + 15;
+        qlo_max = chunk > 0 ? q_last / chunk * chunk : 0;
+        if (window > 0) qlo_max = max(qlo_max, q_last + 1 - window);
     }
 
     for (int it = 0; it < n_kt; ++it) {
@@ -131,16 +138,28 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
             }
         }
         float m_new[2] = {m_run[0], m_run[1]};
+        // a tile that every query of the warp sees whole (after its first key, up to its own position, or kept) skips the mask
+        const bool whole = key0 + MK - 1 <= p0 + warp * 16 && (key0 >= qlo_max || key0 + MK <= keep_first);
+        if (whole) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
-                const bool vis = key <= qpos[i >> 1] && (key >= qlo[i >> 1] || key < keep_first);
-                const float s = vis ? sc[nt][i] * scale : -INFINITY;
-                sc[nt][i] = s;
-                m_new[i >> 1] = fmaxf(m_new[i >> 1], s);
-            }
+                for (int i = 0; i < 4; ++i) {
+                    sc[nt][i] *= scale;
+                    m_new[i >> 1] = fmaxf(m_new[i >> 1], sc[nt][i]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + nt * 8 + 2 * t4 + (i & 1);
+                    const bool vis = key <= qpos[i >> 1] && (key >= qlo[i >> 1] || key < keep_first);
+                    const float s = vis ? sc[nt][i] * scale : -INFINITY;
+                    sc[nt][i] = s;
+                    m_new[i >> 1] = fmaxf(m_new[i >> 1], s);
+                }
+        }
         float corr[2], m_use[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -172,20 +191,30 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const float a = p[h][2 * j], b = p[h][2 * j + 1];
-                        const float ah = __bfloat162float(__float2bfloat16_rn(a)), bh = __bfloat162float(__float2bfloat16_rn(b));
-                        hi[h * 2 + j] = pack_bf16(ah, bh);
-                        lo[h * 2 + j] = pack_bf16(a - ah, b - bh);
+                        const uint32_t top = pack_bf16(a, b);        // both rounded in one conversion; the halves widen by shifts
+                        hi[h * 2 + j] = top;
+                        lo[h * 2 + j] = pack_bf16(a - __uint_as_float(top << 16), b - __uint_as_float(top & 0xffff0000u));
                     }
             }
+            // four value blocks at a time: eight accumulators take the high terms, then the low ones, so that an
+            // MMA does not wait for the one just issued into the same accumulator
 #pragma unroll
-            for (int dd = 0; dd < VD / 16; ++dd) {
-                uint32_t vb[4];
+            for (int d4 = 0; d4 < VD / 16; d4 += 4) {
+                uint32_t vb[4][4];
                 const int row = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldmatrix_x4_trans(vb, v_base + 2 * tile_chunk_offset<VD>(row, dd * 2 + (lane >> 4)));
-                mma_bf16(o[dd * 2], hi, vb[0], vb[1]);
-                mma_bf16(o[dd * 2 + 1], hi, vb[2], vb[3]);
-                mma_bf16(o[dd * 2], lo, vb[0], vb[1]);
-                mma_bf16(o[dd * 2 + 1], lo, vb[2], vb[3]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    ldmatrix_x4_trans(vb[j], v_base + 2 * tile_chunk_offset<VD>(row, (d4 + j) * 2 + (lane >> 4)));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mma_bf16(o[(d4 + j) * 2], hi, vb[j][0], vb[j][1]);
+                    mma_bf16(o[(d4 + j) * 2 + 1], hi, vb[j][2], vb[j][3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mma_bf16(o[(d4 + j) * 2], lo, vb[j][0], vb[j][1]);
+                    mma_bf16(o[(d4 + j) * 2 + 1], lo, vb[j][2], vb[j][3]);
+                }
             }
         }
         __syncthreads();

@@ -469,11 +469,12 @@ moe_down_tc_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const
 
 // ---- a handful of rows (decoding at small batch) ---------------------------------------------------
 // With a few (row, choice) pairs a tile of 64 rows is nearly empty and there are too few tiles to fill the GPU.
-// These kernels take the pairs as they are: a block per (pair, 32 output features), a warp per 4 features, every
-// lane 16 bytes of a weight row at a time against the activation row in shared memory; the weights of an expert
-// that several pairs chose are read again from L2.  bfloat16, K a multiple of 8.
-constexpr int kFewFeatures = 32;
-
+// These kernels take the pairs as they are: a block per (pair, 8 * QF output features), a warp per QF features, every
+// lane 16 bytes of each of its weight rows at a time against the activation row in shared memory.  A warp walks its
+// QF features' rows together, so that 2 QF (gate and up) or QF independent 16-byte loads are under way per lane and
+// step: the launch is bound by the weights it streams, and a lone load per step leaves the memory idle.  QF is 4
+// where that still gives two blocks to an SM, else 2.  The weights of an expert that several pairs chose are read
+// again from L2.  bfloat16, K a multiple of 8.
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
     const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
     float s = 0.f;
@@ -486,6 +487,7 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
 }
 
 // y[pair][F] = act(gate, up) of row pair / top under expert choice[pair]
+template <int QF>
 __global__ void __launch_bounds__(256)
 moe_gate_up_few_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, const int* __restrict__ choice,
                        bf16* __restrict__ y, int D, int F, int top, int n_experts, float limit, float alpha,
@@ -500,35 +502,60 @@ moe_gate_up_few_kernel(const bf16* __restrict__ h, const bf16* __restrict__ W, c
     for (int g = threadIdx.x; g < groups; g += 256) row[g] = src[g];
     __syncthreads();
     const bf16* Wg = W + (size_t)e * 2 * F * D;
+    const int f0 = (blockIdx.x * 8 + warp) * QF;
+    if (f0 >= F) return;
+    const uint4* g_row[QF];
+    const uint4* u_row[QF];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const int f = blockIdx.x * kFewFeatures + warp * 4 + q;
-        if (f >= F) break;
-        const uint4* g_row = reinterpret_cast<const uint4*>(Wg + (size_t)f * D);
-        const uint4* u_row = reinterpret_cast<const uint4*>(Wg + (size_t)(F + f) * D);
-        float sg = 0.f, su = 0.f;
-        for (int g = lane; g < groups; g += 32) {
-            const uint4 x = row[g];
-            sg += dot8(x, g_row[g]);
-            su += dot8(x, u_row[g]);
+    for (int q = 0; q < QF; ++q) {
+        const int f = min(f0 + q, F - 1);                       // a feature beyond the last: read the last again, store nothing
+        g_row[q] = reinterpret_cast<const uint4*>(Wg + (size_t)f * D);
+        u_row[q] = reinterpret_cast<const uint4*>(Wg + (size_t)(F + f) * D);
+    }
+    float sg[QF], su[QF];
+#pragma unroll
+    for (int q = 0; q < QF; ++q) sg[q] = su[q] = 0.f;
+    constexpr int U = 8 / QF;                                   // steps whose loads are issued together: 16 loads a lane
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int g0 = lane; g0 < groups; g0 += 32 * U) {
+        uint4 wg[U][QF], wu[U][QF];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+#pragma unroll
+            for (int q = 0; q < QF; ++q) {
+                wg[u][q] = g < groups ? __ldg(g_row[q] + g) : zero;
+                wu[u][q] = g < groups ? __ldg(u_row[q] + g) : zero;
+            }
         }
-        sg = warp_sum(sg);
-        su = warp_sum(su);
-        if (lane == 0) {
-            if (in_weight) {
-                sg *= in_weight[pair];
-                su *= in_weight[pair];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+            if (g >= groups) break;
+            const uint4 x = row[g];
+#pragma unroll
+            for (int q = 0; q < QF; ++q) {
+                sg[q] += dot8(x, wg[u][q]);
+                su[q] += dot8(x, wu[u][q]);
             }
+        }
+    }
+    const float wt = in_weight ? in_weight[pair] : 1.f;
+#pragma unroll
+    for (int q = 0; q < QF; ++q) {
+        float a = warp_sum(sg[q]) * wt, b = warp_sum(su[q]) * wt;
+        if (lane == 0 && f0 + q < F) {
             if (limit > 0.f) {
-                sg = fminf(sg, limit);
-                su = fminf(fmaxf(su, -limit), limit);
+                a = fminf(a, limit);
+                b = fminf(fmaxf(b, -limit), limit);
             }
-            y[(size_t)pair * F + f] = from_float<bf16>(sg / (1.f + expf(-alpha * sg)) * (su + up_shift));
+            y[(size_t)pair * F + f0 + q] = from_float<bf16>(a / (1.f + expf(-alpha * a)) * (b + up_shift));
         }
     }
 }
 
 // pair_out[pair][D] = weight[pair] * (W_down[e] . y[pair])
+template <int QF>
 __global__ void __launch_bounds__(256)
 moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const int* __restrict__ choice,
                     const float* __restrict__ weight, float* __restrict__ pair_out, int D, int F, int n_experts) {
@@ -543,15 +570,37 @@ moe_down_few_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, cons
     __syncthreads();
     const bf16* Wd = W + (size_t)e * D * F;
     const float wt = weight ? weight[pair] : 1.f;
+    const int n0 = (blockIdx.x * 8 + warp) * QF;
+    if (n0 >= D) return;
+    const uint4* w_row[QF];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const int n = blockIdx.x * kFewFeatures + warp * 4 + q;
-        if (n >= D) break;
-        const uint4* w_row = reinterpret_cast<const uint4*>(Wd + (size_t)n * F);
-        float s = 0.f;
-        for (int g = lane; g < groups; g += 32) s += dot8(row[g], w_row[g]);
-        s = warp_sum(s);
-        if (lane == 0) pair_out[(size_t)pair * D + n] = s * wt;
+    for (int q = 0; q < QF; ++q) w_row[q] = reinterpret_cast<const uint4*>(Wd + (size_t)min(n0 + q, D - 1) * F);
+    float s[QF];
+#pragma unroll
+    for (int q = 0; q < QF; ++q) s[q] = 0.f;
+    constexpr int U = 16 / QF;                                  // steps whose loads are issued together: 16 loads a lane
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int g0 = lane; g0 < groups; g0 += 32 * U) {
+        uint4 w[U][QF];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+#pragma unroll
+            for (int q = 0; q < QF; ++q) w[u][q] = g < groups ? __ldg(w_row[q] + g) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = g0 + 32 * u;
+            if (g >= groups) break;
+            const uint4 x = row[g];
+#pragma unroll
+            for (int q = 0; q < QF; ++q) s[q] += dot8(x, w[u][q]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < QF; ++q) {
+        const float t = warp_sum(s[q]);
+        if (lane == 0 && n0 + q < D) pair_out[(size_t)pair * D + n0 + q] = t * wt;
     }
 }
 
@@ -592,6 +641,17 @@ moe_combine_kernel(const float* __restrict__ pair_out, const int* __restrict__ c
 }
 
 }  // namespace hos
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
 
 using namespace hos;
 
@@ -732,9 +792,20 @@ extern "C" int hos_moe_gate_up_few(const void* h, const void* W, const int* choi
                                    cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (D % 8 || F % 8 || D * 2 > 96 * 1024 || ((uintptr_t)h | (uintptr_t)W | (uintptr_t)y) % 16) return 1;
-    if (D * 2 > 48 * 1024) cudaFuncSetAttribute(moe_gate_up_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 2);
-    launch_pdl(moe_gate_up_few_kernel, dim3((F + kFewFeatures - 1) / kFewFeatures, n_pairs), dim3(256), (size_t)D * 2, stream,
-               (const bf16*)h, (const bf16*)W, choice, (bf16*)y, D, F, top, n_experts, limit, alpha, up_shift, in_weight);
+    const long long want = 2LL * sm_count();
+    const int qf = (long long)((F + 31) / 32) * n_pairs >= want ? 4 : (long long)((F + 15) / 16) * n_pairs >= want ? 2 : 1;
+#define HOS_GU_FEW(QF)                                                                                               \
+    do {                                                                                                             \
+        if (D * 2 > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(moe_gate_up_few_kernel<QF>, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 2);    \
+        launch_pdl(moe_gate_up_few_kernel<QF>, dim3((F + 8 * QF - 1) / (8 * QF), n_pairs), dim3(256), (size_t)D * 2, \
+                   stream, (const bf16*)h, (const bf16*)W, choice, (bf16*)y, D, F, top, n_experts, limit, alpha,     \
+                   up_shift, in_weight);                                                                             \
+    } while (0)
+    if (qf == 4) HOS_GU_FEW(4);
+    else if (qf == 2) HOS_GU_FEW(2);
+    else HOS_GU_FEW(1);
+#undef HOS_GU_FEW
     return check_launch("moe_gate_up_few");
 }
 
@@ -742,8 +813,18 @@ extern "C" int hos_moe_down_few(const void* y, const void* W, const int* choice,
                                 int n_pairs, int D, int F, int n_experts, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (D % 8 || F % 8 || F * 2 > 96 * 1024 || ((uintptr_t)y | (uintptr_t)W) % 16) return 1;
-    if (F * 2 > 48 * 1024) cudaFuncSetAttribute(moe_down_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F * 2);
-    launch_pdl(moe_down_few_kernel, dim3((D + kFewFeatures - 1) / kFewFeatures, n_pairs), dim3(256), (size_t)F * 2, stream,
-               (const bf16*)y, (const bf16*)W, choice, weight, pair_out, D, F, n_experts);
+    const long long want = 2LL * sm_count();
+    const int qf = (long long)((D + 31) / 32) * n_pairs >= want ? 4 : (long long)((D + 15) / 16) * n_pairs >= want ? 2 : 1;
+#define HOS_DOWN_FEW(QF)                                                                                             \
+    do {                                                                                                             \
+        if (F * 2 > 48 * 1024)                                                                                       \
+            cudaFuncSetAttribute(moe_down_few_kernel<QF>, cudaFuncAttributeMaxDynamicSharedMemorySize, F * 2);       \
+        launch_pdl(moe_down_few_kernel<QF>, dim3((D + 8 * QF - 1) / (8 * QF), n_pairs), dim3(256), (size_t)F * 2,    \
+                   stream, (const bf16*)y, (const bf16*)W, choice, weight, pair_out, D, F, n_experts);               \
+    } while (0)
+    if (qf == 4) HOS_DOWN_FEW(4);
+    else if (qf == 2) HOS_DOWN_FEW(2);
+    else HOS_DOWN_FEW(1);
+#undef HOS_DOWN_FEW
     return check_launch("moe_down_few");
 }
