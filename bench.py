@@ -465,6 +465,9 @@ def fobilorn_kernel_work(z, tokens, batch, ctx):
                             "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * ff * width)},
         "hos_moe_down": {"prefill": (E * ff * width * 2, 2.0 * tokens * top * ff * width),
                          "decode": (touched * ff * width * 2, 2.0 * batch * top * ff * width)},
+        # the few-rows forms of both (a handful of pairs): the weights of the experts that were chosen
+        "hos_moe_gate_up_few": {"prefill": (0, 0.0), "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * ff * width)},
+        "hos_moe_down_few": {"prefill": (0, 0.0), "decode": (touched * ff * width * 2, 2.0 * batch * top * ff * width)},
         "hos_moe_combine": {"prefill": (tokens * width * (4 * top + 2 + 4), 0.0), "decode": (batch * width * (4 * top + 2 + 4), 0.0)},
     }
 

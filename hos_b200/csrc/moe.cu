@@ -472,8 +472,10 @@ moe_down_tc_kernel(const bf16* __restrict__ y, const bf16* __restrict__ W, const
 // These kernels take the pairs as they are: a block per (pair, 8 * QF output features), a warp per QF features, every
 // lane 16 bytes of each of its weight rows at a time against the activation row in shared memory.  A warp walks its
 // QF features' rows together, so that 2 QF (gate and up) or QF independent 16-byte loads are under way per lane and
-// step: the launch is bound by the weights it streams, and a lone load per step leaves the memory idle.  QF is 4
-// where that still gives two blocks to an SM, else 2.  The weights of an expert that several pairs chose are read
+// step, and the loads of several steps are issued together (16 a lane): the launch is bound by the weights it
+// streams, and a lone load per step leaves the memory idle.  QF is the largest of 4, 2, 1 that still gives two
+// blocks to an SM (fewer blocks of more features leave SMs idle or with twice the work of others; more blocks of
+// fewer features read the activation row more often).  The weights of an expert that several pairs chose are read
 // again from L2.  bfloat16, K a multiple of 8.
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
     const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};

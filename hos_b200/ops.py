@@ -750,15 +750,25 @@ def moe_few(h, w_gate_up, w_down, choice, weight, y, pair_out, top: int, n_exper
     lib = experts()
     global launch_count
     pairs, d, f = choice.numel(), h.shape[1], w_down.shape[2]
-    rc = lib.fn("hos_moe_gate_up_few")(_ptr(h), _ptr(w_gate_up), _ptr(choice), _ptr(y), pairs, d, f, int(top), int(n_experts),
-                                       float(limit), float(alpha), float(up_shift),
-                                       _ptr(weight) if weight_on_input else None, _stream())
+
+    def timed(name, *args):                 # these calls may answer 1 (not their sizes), so they do not go through call()
+        if _call_times is None:
+            return lib.fn(name)(*args)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = lib.fn(name)(*args)
+        e1.record()
+        if rc == 0:
+            _call_times.append((name, e0, e1))
+        return rc
+
+    rc = timed("hos_moe_gate_up_few", _ptr(h), _ptr(w_gate_up), _ptr(choice), _ptr(y), pairs, d, f, int(top), int(n_experts),
+               float(limit), float(alpha), float(up_shift), _ptr(weight) if weight_on_input else None, _stream())
     if rc == 1:
         return False
     if rc == 0:
-        rc = lib.fn("hos_moe_down_few")(_ptr(y), _ptr(w_down), _ptr(choice), None if weight_on_input else _ptr(weight),
-                                        _ptr(pair_out), pairs, d, f,
-                                        int(n_experts), _stream())
+        rc = timed("hos_moe_down_few", _ptr(y), _ptr(w_down), _ptr(choice), None if weight_on_input else _ptr(weight),
+                   _ptr(pair_out), pairs, d, f, int(n_experts), _stream())
     launch_count += 2
     if rc != 0:
         msg = lib._last_error() if lib._last_error else b""

@@ -605,3 +605,50 @@ def test_the_router_kernel_alone_against_float64():
                 w1 = torch.empty(top, device=dev)
                 ops.moe_route(h[n - 1:].clone(), router, None, seq[:1], c1, w1, top, ops.MOE_SCORING["logistic"])
                 assert torch.equal(c1.cpu(), choice[n - 1]) and torch.equal(w1.cpu(), weight[n - 1]), "alone and in a batch differ"
+
+
+@pytest.mark.gpu
+def test_the_few_rows_expert_products_alone_against_float64():
+    """A handful of (row, choice) pairs without lists or tiles: one, two or four features to a warp (the grid decides),
+    widths and feature counts that end inside a warp's share and inside a round of loads, the weight on the expert's
+    input or on its output, a clamp and a shift or none, a pair that chose nothing."""
+    from hos_b200 import ops
+    dev = "cuda"
+    torch.manual_seed(21)
+    for rows, top, n_experts, d, f, on_input, limit, alpha, shift in (
+            (1, 4, 9, 1024, 1024, True, 0.0, 1.0, 0.0),        # few blocks: one feature to a warp
+            (3, 2, 5, 1000, 1016, True, 0.0, 1.0, 0.0),        # two to a warp; rows of 125 groups
+            (8, 4, 6, 520, 2408, True, 0.0, 1.0, 0.0),         # four to a warp; features end inside a block
+            (2, 3, 4, 72, 40, False, 7.0, 1.7, 1.0),           # tiny, the weight on the output, clamp and shift
+            (5, 2, 3, 4096, 264, False, 0.0, 1.0, 0.0)):
+        pairs = rows * top
+        h = torch.randn(rows, d, device=dev).to(torch.bfloat16)
+        w_gu = (torch.randn(n_experts, 2 * f, d, device=dev) / d ** 0.5).to(torch.bfloat16)
+        w_dn = (torch.randn(n_experts, d, f, device=dev) / f ** 0.5).to(torch.bfloat16)
+        choice = torch.randint(0, n_experts, (pairs,), dtype=torch.int32, device=dev)
+        if pairs > 2:
+            choice[1] = -1
+        weight = torch.rand(pairs, device=dev) + 0.25
+        y = torch.zeros(pairs, f, dtype=torch.bfloat16, device=dev)
+        out = torch.full((pairs, d), -5.0, device=dev)
+        assert ops.moe_few(h, w_gu, w_dn, choice, weight, y, out, top, n_experts, limit, alpha, shift, weight_on_input=on_input)
+        torch.cuda.synchronize()
+        for p in range(pairs):
+            e = int(choice[p])
+            if e < 0:
+                assert float(out[p].min()) == -5.0 and float(out[p].max()) == -5.0      # untouched
+                continue
+            x = h[p // top].double().cpu()
+            wt = float(weight[p])
+            g = w_gu[e, :f].double().cpu() @ x
+            u = w_gu[e, f:].double().cpu() @ x
+            if on_input:
+                g, u = g * wt, u * wt
+            if limit > 0:
+                g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+            act = g * torch.sigmoid(alpha * g) * (u + shift)
+            assert float((y[p].double().cpu() - act).abs().max()) < 0.02 * float(act.abs().max()) + 1e-3, (rows, d, f, p)
+            down = w_dn[e].double().cpu() @ y[p].double().cpu()             # from the rounded activations the kernel read
+            if not on_input:
+                down = down * wt
+            assert float((out[p].double().cpu() - down).abs().max()) < 1e-4 * float(down.abs().max()) + 1e-5, (rows, d, f, p)
