@@ -31,7 +31,7 @@ __device__ __forceinline__ float4 route_load4(const bf16* p) {
                        __uint_as_float(u.y & 0xffff0000u));
 }
 
-// One warp: z [n_out] logits of row n (in shared memory) -> scores in place, the `top` largest of (score + correction)
+// One warp: z [n_out] logits of row n (in shared memory) -> scores, the `top` largest of (score + correction)
 // and their plain scores.  A padding row (token_seq < 0) chooses nothing.
 __device__ __forceinline__ void route_choose(float* z, float* taken, const float* __restrict__ correction,
                                              const int* __restrict__ token_seq, int* __restrict__ choice,
@@ -43,7 +43,11 @@ __device__ __forceinline__ void route_choose(float* z, float* taken, const float
         }
         return;
     }
-    if (scoring == 1) {
+    // Logistic scores without a correction are ranked by their logits: the order is the scores' own, and it still tells
+    // apart logits whose scores round to the same 32-bit number near 1.
+    const bool by_logit = scoring == 1 && correction == nullptr;
+    if (by_logit) {
+    } else if (scoring == 1) {
         for (int e = lane; e < n_out; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
     } else {
         float m = -INFINITY;
@@ -82,7 +86,7 @@ __device__ __forceinline__ void route_choose(float* z, float* taken, const float
         if (lane == 0) {
             const bool ok = arg != 0x7fffffff;
             choice[(size_t)n * top + k] = ok ? arg : -1;
-            weight[(size_t)n * top + k] = ok ? z[arg] : 0.f;
+            weight[(size_t)n * top + k] = ok ? (by_logit ? 1.f / (1.f + expf(-z[arg])) : z[arg]) : 0.f;
             if (ok) taken[arg] = 1.f;
         }
         __syncwarp();

@@ -652,3 +652,31 @@ def test_the_few_rows_expert_products_alone_against_float64():
             if not on_input:
                 down = down * wt
             assert float((out[p].double().cpu() - down).abs().max()) < 1e-4 * float(down.abs().max()) + 1e-5, (rows, d, f, p)
+
+
+@pytest.mark.gpu
+def test_the_router_tells_apart_scores_that_round_to_the_same_number():
+    """Logits of 10 to 40 have logistic scores within a few 32-bit steps of 1 (or equal to it); the chosen experts are
+    still those with the largest logits, as they are with exact scores."""
+    from hos_b200 import ops
+    dev = "cuda"
+    torch.manual_seed(5)
+    n, d, n_out, top = 40, 128, 24, 5
+    router = torch.randn(n_out, d, device=dev) * (6.0 / d ** 0.5)
+    h = torch.randn(n, d, device=dev)
+    h[:, 0] = 25.0 / (6.0 / d ** 0.5)                                      # lifts every logit by 25 x the router's first column
+    router[:, 0] = 6.0 / d ** 0.5
+    seq = torch.zeros(n, dtype=torch.int32, device=dev)
+    choice = torch.empty(n * top, dtype=torch.int32, device=dev)
+    weight = torch.empty(n * top, device=dev)
+    ops.moe_route(h, router, None, seq, choice, weight, top, ops.MOE_SCORING["logistic"])
+    z = h.double().cpu() @ router.double().cpu().T
+    assert float(z.min()) > 4.0
+    choice = choice.cpu().view(n, top)
+    for r in range(n):
+        order = torch.argsort(z[r], descending=True)
+        gap = float(z[r, order[top - 1]] - z[r, order[top]])
+        if gap < 1e-3:
+            continue                                                       # a close call in 32-bit logits too
+        assert sorted(choice[r].tolist()) == sorted(order[:top].tolist()), r
+    assert float(weight.min()) > 0.98
