@@ -656,7 +656,7 @@ def test_the_few_rows_expert_products_alone_against_float64():
 
 @pytest.mark.gpu
 def test_the_router_tells_apart_scores_that_round_to_the_same_number():
-    """Logits of 10 to 40 have logistic scores within a few 32-bit steps of 1 (or equal to it); the chosen experts are
+    """Logits of 10 to 50 have logistic scores within a few 32-bit steps of 1 (or equal to it); the chosen experts are
     still those with the largest logits, as they are with exact scores."""
     from hos_b200 import ops
     dev = "cuda"
@@ -664,7 +664,7 @@ def test_the_router_tells_apart_scores_that_round_to_the_same_number():
     n, d, n_out, top = 40, 128, 24, 5
     router = torch.randn(n_out, d, device=dev) * (6.0 / d ** 0.5)
     h = torch.randn(n, d, device=dev)
-    h[:, 0] = 25.0 / (6.0 / d ** 0.5)                                      # lifts every logit by 25 x the router's first column
+    h[:, 0] = 32.0 / (6.0 / d ** 0.5)                                      # with the router's first column: 32 added to every logit
     router[:, 0] = 6.0 / d ** 0.5
     seq = torch.zeros(n, dtype=torch.int32, device=dev)
     choice = torch.empty(n * top, dtype=torch.int32, device=dev)
