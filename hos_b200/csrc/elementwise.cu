@@ -551,6 +551,23 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     out[n * F + f] = from_float<T>(a * u);
 }
 
+// The clamped form on 32-bit gate|up rows: g = min(g, limit), u = clamp(u, -limit, limit) (limit <= 0: no clamp),
+// out = g logistic(alpha g) (u + shift), rounded to the output's type once.
+template <typename TO>
+__global__ void clamped_gated_act_kernel(const float* __restrict__ gu, TO* __restrict__ out, int F, float limit, float alpha,
+                                         float shift) {
+    pdl_enter();
+    const size_t n = blockIdx.x;
+    const int f = blockIdx.y * blockDim.x + threadIdx.x;
+    if (f >= F) return;
+    float g = gu[n * 2 * F + f], u = gu[n * 2 * F + F + f];
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    out[n * F + f] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + shift));
+}
+
 // ---- row gather ----------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
                                    float* __restrict__ out, int D) {
@@ -768,6 +785,18 @@ extern "C" int hos_gated_act(const void* gu, void* out, int dtype, int N, int F,
     else if (dtype == kBF16) launch_pdl(gated_act_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, F, act);
     else HOS_REFUSE("gated_act: unknown dtype %d", dtype);
     return check_launch("gated_act");
+}
+
+extern "C" int hos_clamped_gated_act(const float* gu, void* out, int out_dtype, int N, int F, float limit, float alpha,
+                                     float shift, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    dim3 grid(N, (F + 255) / 256);
+    if (out_dtype == kF32)
+        launch_pdl(clamped_gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, gu, (float*)out, F, limit, alpha, shift);
+    else if (out_dtype == kBF16)
+        launch_pdl(clamped_gated_act_kernel<bf16>, dim3(grid), dim3(256), 0, stream, gu, (bf16*)out, F, limit, alpha, shift);
+    else HOS_REFUSE("clamped_gated_act: unknown dtype %d", out_dtype);
+    return check_launch("clamped_gated_act");
 }
 
 extern "C" int hos_gather_rows(const float* x, const int* idx, float* out, int n, int D,

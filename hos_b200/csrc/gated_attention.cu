@@ -42,14 +42,14 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
                const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims, float magnitude,
                const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                float* __restrict__ q_out, PagedKV2 cache, int H, int G, int kd, int vd, int norm_whole,
-               const float* __restrict__ v_first, long long v_first_ld, float v_mix) {
+               const float* __restrict__ v_first, long long v_first_ld, float v_mix, int q_maps) {
     pdl_enter();
     __shared__ float scratch[32];
     const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = token_seq[n];
     const float* row = proj + (size_t)n * ld;
     if (seq < 0) {
-        for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q_out[(size_t)n * H * kd + i] = 0.f;
+        for (int i = threadIdx.x; i < H * kd * q_maps; i += blockDim.x) q_out[(size_t)n * H * kd * q_maps + i] = 0.f;
         return;
     }
     const int pos = token_pos[n];
@@ -105,7 +105,18 @@ qk_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__
                 v[i] = (d & 1) ? fmaf(v[i], cs, other * sn) : fmaf(v[i], cs, -other * sn);
             }
         }
-        if (is_q) {
+        if (is_q && q_maps > 1) {
+            // a head's kd numbers are q_maps queries of kd / q_maps numbers each, one per attention map over the same
+            // key row: query m is written as a head of its own, zero outside its own part of the key row
+            const int md = kd / q_maps;
+            float* qo = q_out + ((size_t)n * H + item) * q_maps * kd;
+            for (int m = 0; m < q_maps; ++m)
+#pragma unroll
+                for (int i = 0; i < kPrepPL; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < kd) qo[(size_t)m * kd + d] = d / md == m ? v[i] : 0.f;
+                }
+        } else if (is_q) {
             float* qo = q_out + ((size_t)n * H + item) * kd;
 #pragma unroll
             for (int i = 0; i < kPrepPL; ++i) {
@@ -358,6 +369,40 @@ attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ 
     }
 }
 
+// Two attention maps over the same values, combined: a [N][H][2][vd] float32 (map 1 and map 2 of a head side by side);
+// out[n][h][:] = rms_norm(a1 - lambda a2) * mult * logistic(gate[n][h * vd + :]); the root mean square is per head
+// (eps inside the root, no weight).  A warp per (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const float* __restrict__ a, float lambda, float mult, float eps, const float* __restrict__ gate,
+                    long long gate_stride, const int* __restrict__ token_seq, TO* __restrict__ out, int N, int H, int vd) {
+    pdl_enter();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)N * H) return;
+    const int n = (int)(item / H), h = (int)(item % H);
+    TO* op = out + (size_t)item * vd;
+    if (token_seq[n] < 0) {
+        for (int d = lane; d < vd; d += 32) op[d] = from_float<TO>(0.f);
+        return;
+    }
+    const float* a1 = a + (size_t)item * 2 * vd;
+    const float* a2 = a1 + vd;
+    float ss = 0.f;
+    for (int d = lane; d < vd; d += 32) {
+        const float o = fmaf(-lambda, a2[d], a1[d]);
+        ss = fmaf(o, o, ss);
+    }
+    ss = warp_sum(ss);
+    const float f = mult / sqrtf(ss / (float)vd + eps);
+    const float* gt = gate != nullptr ? gate + (size_t)n * gate_stride + (size_t)h * vd : nullptr;
+    for (int d = lane; d < vd; d += 32) {
+        float o = fmaf(-lambda, a2[d], a1[d]) * f;
+        if (gt != nullptr) o *= 1.f / (1.f + expf(-gt[d]));
+        op[d] = from_float<TO>(o);
+    }
+}
+
 }  // namespace hos
 
 using namespace hos;
@@ -368,12 +413,15 @@ extern "C" const char* hos_last_error() { return error_buffer(); }
 // call's cache passes G = 0 and projects neither), then whatever else the caller keeps there.  bias: the same
 // columns' biases or null.  q_norm / k_norm: [kd] or null (norm_whole: [H * kd] and [G * kd]).  freq: [rot_dims / 2] or
 // null.  v_first: row n's values of another layer at v_first[n * v_first_ld + ...] (G * vd numbers), or null.
+// q_maps > 1: q_out is [N][H * q_maps][kd]: each head's kd numbers are q_maps queries, written as heads of their own.
 extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const float* q_norm, const float* k_norm, float eps,
                            const float* freq, int rot_dims, float magnitude, const int* token_pos, const int* token_seq,
                            const int* seq_slot, float* q_out, void* k_pages, void* v_pages, int cache_dtype,
                            const int* page_table, int table_stride, int ring_pages, int N, int H, int G, int kd, int vd,
-                           int norm_whole, const float* v_first, long long v_first_ld, float v_mix, cudaStream_t stream) {
+                           int norm_whole, const float* v_first, long long v_first_ld, float v_mix, int q_maps,
+                           cudaStream_t stream) {
     if (N <= 0) return 0;
+    if (q_maps < 1 || kd % q_maps != 0) HOS_REFUSE("qk_prep: heads of %d numbers do not hold %d queries", kd, q_maps);
     if (kd <= 0 || kd > 32 * kPrepMaxPL) HOS_REFUSE("qk_prep: heads of %d numbers are outside 1..%d", kd, 32 * kPrepMaxPL);
     if (freq == nullptr) rot_dims = 0;
     if (rot_dims % 2 != 0 || rot_dims > kd) HOS_REFUSE("qk_prep: %d rotated numbers in heads of %d", rot_dims, kd);
@@ -383,7 +431,7 @@ extern "C" int hos_qk_prep(const float* proj, int ld, const float* bias, const f
 #define HOS_QKP_N(TC, PL, NT)                                                                                        \
     launch_pdl(qk_prep_kernel<TC, PL, NT>, dim3(N), dim3(NT), 0, stream, proj, ld, bias, q_norm, k_norm, eps, freq,   \
                rot_dims, magnitude, token_pos, token_seq, seq_slot, q_out, c, H, G, kd, vd, norm_whole, v_first,     \
-               v_first_ld, v_mix)
+               v_first_ld, v_mix, q_maps)
 #define HOS_QKP(TC, PL)                                                                                              \
     do {                                                                                                             \
         if (wide) HOS_QKP_N(TC, PL, 512);                                                                            \
@@ -472,4 +520,21 @@ extern "C" int hos_attn_merge(const float* part_acc, const float* part_ml, int n
     launch_pdl(attn_merge_kernel, dim3((unsigned)(((long long)N * H + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml,
                n_splits, gate, gate_stride, token_seq, out, out_dtype == kBF16 ? 1 : 0, N, H, vd);
     return check_launch("attn_merge");
+}
+
+// a: float32 [N][H][2][vd], the two maps' outputs of every head; out: [N][H][vd] of out_dtype; gate: row n's logits for
+// the H * vd output columns at gate[n * gate_stride + ...], or null.
+extern "C" int hos_diff_combine(const float* a, float lambda, float mult, float eps, const float* gate, long long gate_stride,
+                                const int* token_seq, void* out, int out_dtype, int N, int H, int vd, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const unsigned blocks = (unsigned)(((long long)N * H + 3) / 4);
+    if (out_dtype == kBF16)
+        launch_pdl(diff_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, a, lambda, mult, eps, gate, gate_stride,
+                   token_seq, (bf16*)out, N, H, vd);
+    else if (out_dtype == kF32)
+        launch_pdl(diff_combine_kernel<float>, dim3(blocks), dim3(128), 0, stream, a, lambda, mult, eps, gate, gate_stride,
+                   token_seq, (float*)out, N, H, vd);
+    else
+        HOS_REFUSE("diff_combine: unknown dtype %d", out_dtype);
+    return check_launch("diff_combine");
 }

@@ -30,7 +30,8 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
                       const int* __restrict__ page_table, int table_stride, int ring_pages, const float* __restrict__ sink,
                       const float* __restrict__ gate, long long gate_stride, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-                      bf16* __restrict__ out, int n_seqs, int H, int G, float scale, int chunk, int window, int keep_first) {
+                      void* __restrict__ out_v, int out_f32, int n_seqs, int H, int G, float scale, int chunk, int window,
+                      int keep_first) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [64][KD]
@@ -232,7 +233,14 @@ gated_attn_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pa
         const size_t row = (size_t)(row0 + q0 + qi);
         float f = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
         if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[row * gate_stride + head]));
-        bf16* op = out + (row * H + head) * VD;
+        if (out_f32) {          // a caller that goes on computing with the heads' outputs takes them unrounded
+            float* op = (float*)out_v + (row * H + head) * VD;
+#pragma unroll
+            for (int i = 0; i < VD / 8; ++i)
+                *reinterpret_cast<float2*>(op + i * 8 + 2 * t4) = make_float2(o[i][2 * r] * f, o[i][2 * r + 1] * f);
+            continue;
+        }
+        bf16* op = (bf16*)out_v + (row * H + head) * VD;
 #pragma unroll
         for (int i = 0; i < VD / 8; ++i)
             *reinterpret_cast<uint32_t*>(op + i * 8 + 2 * t4) = pack_bf16(o[i][2 * r] * f, o[i][2 * r + 1] * f);
@@ -251,9 +259,9 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
                              const int* __restrict__ page_table, int table_stride, int ring_pages,
                              const float* __restrict__ sink, const float* __restrict__ gate, long long gate_stride,
                              const int* __restrict__ token_pos, const int* __restrict__ token_seq,
-                             const int* __restrict__ seq_slot, bf16* __restrict__ out, float* __restrict__ part_acc,
-                             float* __restrict__ part_ml, int n_splits, int H, int G, float scale, int chunk, int window,
-                             int keep_first) {
+                             const int* __restrict__ seq_slot, void* __restrict__ out_v, int out_f32,
+                             float* __restrict__ part_acc, float* __restrict__ part_ml, int n_splits, int H, int G,
+                             float scale, int chunk, int window, int keep_first) {
     pdl_enter();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [16][KD]
@@ -266,7 +274,10 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
     if (seq < 0) {                                                  // padding: defined rows, nothing read
         for (int idx = threadIdx.x; idx < QH * VD; idx += 128) {
             const size_t hrow = (size_t)n * H + h0 + idx / VD;
-            if (n_splits == 1) out[hrow * VD + idx % VD] = from_float<bf16>(0.f);
+            if (n_splits == 1) {
+                if (out_f32) ((float*)out_v)[hrow * VD + idx % VD] = 0.f;
+                else ((bf16*)out_v)[hrow * VD + idx % VD] = from_float<bf16>(0.f);
+            }
             else if (idx % VD == 0) {
                 part_ml[(hrow * n_splits + split) * 2] = -INFINITY;
                 part_ml[(hrow * n_splits + split) * 2 + 1] = 0.f;
@@ -442,7 +453,8 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
         if (n_splits == 1) {
             float f = L > 0.f ? 1.f / L : 0.f;
             if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)n * gate_stride + h0 + row]));
-            out[hrow * VD + d] = from_float<bf16>(A * f);
+            if (out_f32) ((float*)out_v)[hrow * VD + d] = A * f;
+            else ((bf16*)out_v)[hrow * VD + d] = from_float<bf16>(A * f);
         } else {
             part_acc[(hrow * n_splits + split) * VD + d] = A;
             if (d == 0) {
@@ -458,17 +470,18 @@ gated_attn_mma_decode_kernel(const float* __restrict__ q, const bf16* __restrict
 using namespace hos;
 
 // Head sizes of 64 or 128 numbers each (the caller runs the other kernel for the rest).
-// q: float32 [N][H][kd]; out: bfloat16 [N][H][vd]; n_q_tiles: at least the sum over sequences of ceil(rows / 64).
+// q: float32 [N][H][kd]; out: [N][H][vd], bfloat16 or (out_f32) float32; n_q_tiles: at least the sum over sequences of
+// ceil(rows / 64).
 extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                                   int table_stride, int ring_pages, const float* sink, const float* gate,
                                   long long gate_stride, const int* cu_seqlens, const int* token_pos, const int* token_seq,
-                                  const int* seq_slot, void* out, int n_seqs, int n_q_tiles, int H, int G, int kd, int vd,
+                                  const int* seq_slot, void* out, int out_f32, int n_seqs, int n_q_tiles, int H, int G, int kd, int vd,
                                   float scale, int chunk, int window, int keep_first, cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0) return 0;
     if (G <= 0 || H % G != 0 || H > 65535) HOS_REFUSE("gated_attn_mma: %d heads over %d kv heads", H, G);
     if ((kd != 64 && kd != 128) || (vd != 64 && vd != 128))
         HOS_REFUSE("gated_attn_mma: heads of %d and %d numbers (64 or 128 are compiled)", kd, vd);
-    if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % 4))
+    if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)out % (out_f32 ? 8 : 4)))
         HOS_REFUSE("gated_attn_mma: rows and pages must be 16-byte aligned");
     const dim3 grid(n_q_tiles, H);
 #define HOS_GAM(KDv, VDv)                                                                                            \
@@ -481,7 +494,7 @@ extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const voi
         }                                                                                                            \
         launch_pdl(gated_attn_mma_kernel<KDv, VDv>, grid, dim3(128), smem, stream, q, (const bf16*)k_pages,          \
                    (const bf16*)v_pages, page_table, table_stride, ring_pages, sink, gate, gate_stride, cu_seqlens,  \
-                   token_pos, token_seq, seq_slot, (bf16*)out, n_seqs, H, G, scale, chunk, window, keep_first);      \
+                   token_pos, token_seq, seq_slot, out, out_f32, n_seqs, H, G, scale, chunk, window, keep_first);    \
     } while (0)
     if (kd == 64 && vd == 64) HOS_GAM(64, 64);
     else if (kd == 64) HOS_GAM(64, 128);
@@ -491,13 +504,13 @@ extern "C" int hos_gated_attn_mma(const float* q, const void* k_pages, const voi
     return check_launch("gated_attn_mma");
 }
 
-// Single tokens: q float32 [N][H][kd], out bfloat16 [N][H][vd]; up to 16 query heads to a kv head.  With n_splits > 1 the
+// Single tokens: q float32 [N][H][kd], out [N][H][vd] bfloat16 or (out_f32) float32; up to 16 query heads to a kv head.  With n_splits > 1 the
 // shares' partial results go to part_acc [N][H][n_splits][vd] and part_ml [N][H][n_splits][2] for hos_attn_merge.
 extern "C" int hos_gated_attn_mma_decode(const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                                          int table_stride, int ring_pages, const float* sink, const float* gate,
                                          long long gate_stride, const int* token_pos, const int* token_seq,
-                                         const int* seq_slot, void* out, float* part_acc, float* part_ml, int n_splits,
-                                         int N, int H, int G, int kd, int vd, float scale, int chunk, int window,
+                                         const int* seq_slot, void* out, int out_f32, float* part_acc, float* part_ml,
+                                         int n_splits, int N, int H, int G, int kd, int vd, float scale, int chunk, int window,
                                          int keep_first, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (G <= 0 || H % G != 0 || H / G > 16 || G > 65535) HOS_REFUSE("gated_attn_mma_decode: %d heads over %d kv heads", H, G);
@@ -517,7 +530,7 @@ extern "C" int hos_gated_attn_mma_decode(const float* q, const void* k_pages, co
         }                                                                                                            \
         launch_pdl(gated_attn_mma_decode_kernel<KDv, VDv>, grid, dim3(128), smem, stream, q, (const bf16*)k_pages,   \
                    (const bf16*)v_pages, page_table, table_stride, ring_pages, sink, gate, gate_stride, token_pos,   \
-                   token_seq, seq_slot, (bf16*)out, part_acc, part_ml, n_splits, H, G, scale, chunk, window,         \
+                   token_seq, seq_slot, out, out_f32, part_acc, part_ml, n_splits, H, G, scale, chunk, window,       \
                    keep_first);                                                                                      \
     } while (0)
     if (kd == 64 && vd == 64) HOS_GAD(64, 64);

@@ -28,7 +28,8 @@ namespace hos {
 // proj[n] = [ q: H heads of (dq + P) | c_raw: R | key_rot_raw: P ].  Writes
 //   kc[n]     = [ rms(c_raw) * w_norm | rot(key_rot_raw) ]                (the row the cache keeps)
 //   q_lat[n][h][R : R + P] = rot(q_h[dq : dq + P])                        (32-bit)
-// and stores kc[n] at the token's place in the paged cache (rows of D, not permuted).
+// and stores kc[n] at the token's place in the paged cache (rows of D, not permuted).  With kc null the rows hold
+// the queries only (a call that reads another call's cache): nothing is normed or stored.
 // Rotation: the first rot_dims of the P numbers, pairs (2i, 2i + 1), angle = position * inv_freq[i].
 template <typename T>
 __global__ void latent_prep_kernel(const T* __restrict__ proj, int proj_stride, int H, int dq, int R, int P,
@@ -56,23 +57,26 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int proj_stride, 
     }
     const T* row = proj + (size_t)n * proj_stride;
     const T* craw = row + (size_t)H * (dq + P);
+    const bool keys = kc != nullptr;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-        const float v = to_float(craw[d]);
-        ss = fmaf(v, v, ss);
-    }
+    if (keys)
+        for (int d = threadIdx.x; d < R; d += blockDim.x) {
+            const float v = to_float(craw[d]);
+            ss = fmaf(v, v, ss);
+        }
     const float rinv = rsqrtf(block_sum(ss, scratch) / (float)R + eps);      // (also orders sincos_tab)
-    T* out = kc + (size_t)n * D;
+    T* out = keys ? kc + (size_t)n * D : nullptr;
     T* cached = page >= 0 ? k_pages + ((size_t)page * kPageTokens + pos % kPageTokens) * D : nullptr;
-    for (int d = threadIdx.x; d < R; d += blockDim.x) {
-        const T v = from_float<T>(to_float(craw[d]) * rinv * w_norm[d]);
-        out[d] = v;
-        if (cached) cached[d] = v;
-    }
+    if (keys)
+        for (int d = threadIdx.x; d < R; d += blockDim.x) {
+            const T v = from_float<T>(to_float(craw[d]) * rinv * w_norm[d]);
+            out[d] = v;
+            if (cached) cached[d] = v;
+        }
     // the shared rotated key part, then every head's rotated query part: items of one pair (or one
     // unrotated number beyond rot_dims)
     const int per = half + (P - rot_dims);
-    for (int it = threadIdx.x; it < (H + 1) * per; it += blockDim.x) {
+    for (int it = threadIdx.x; it < (H + (keys ? 1 : 0)) * per; it += blockDim.x) {
         const int who = it / per, j = it - who * per;       // who == H: the key
         const T* src = who == H ? craw + R : row + (size_t)who * (dq + P) + dq;
         float a, b = 0.f;

@@ -35,7 +35,8 @@ __device__ __forceinline__ float4 route_load4(const bf16* p) {
 // and their plain scores.  A padding row (token_seq < 0) chooses nothing.
 __device__ __forceinline__ void route_choose(float* z, float* taken, const float* __restrict__ correction,
                                              const int* __restrict__ token_seq, int* __restrict__ choice,
-                                             float* __restrict__ weight, int n, int n_out, int top, int scoring, int lane) {
+                                             float* __restrict__ weight, int n, int n_out, int top, int scoring, int lane,
+                                             float renorm, float wscale) {
     if (token_seq[n] < 0) {
         for (int k = lane; k < top; k += 32) {
             choice[(size_t)n * top + k] = -1;
@@ -91,6 +92,16 @@ __device__ __forceinline__ void route_choose(float* z, float* taken, const float
         }
         __syncwarp();
     }
+    // renorm >= 0: the chosen scores are divided by their sum (+ renorm); then every weight times wscale
+    if (lane == 0 && (renorm >= 0.f || wscale != 1.f)) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += weight[(size_t)n * top + k];
+        for (int k = 0; k < top; ++k) {
+            float w = weight[(size_t)n * top + k];
+            if (renorm >= 0.f) w = w / (sum + renorm);
+            weight[(size_t)n * top + k] = w * wscale;
+        }
+    }
 }
 
 // A block takes RT rows, so that the 32-bit router matrix is read once for all of them.  Every thread takes a slice of
@@ -101,7 +112,7 @@ template <typename T, int RT, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
                  const int* __restrict__ token_seq, int* __restrict__ choice, float* __restrict__ weight, int N, int D,
-                 int n_out, int top, int scoring, float* __restrict__ logits) {
+                 int n_out, int top, int scoring, float* __restrict__ logits, float renorm, float wscale) {
     pdl_enter();
     extern __shared__ float route_sm[];
     float* z_all = route_sm;                       // [RT][n_out] scores
@@ -181,13 +192,14 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
     const int n = n0 + warp;
     if (n >= N) return;
     route_choose(z_all + warp * n_out, taken_all + warp * n_out, correction, token_seq, choice, weight, n, n_out, top, scoring,
-                 lane);
+                 lane, renorm, wscale);
 }
 
 // A warp per row: logits [N][n_out] from moe_route_kernel's blocks -> scores, the `top` largest, their weights.
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ correction, const int* __restrict__ token_seq,
-                  int* __restrict__ choice, float* __restrict__ weight, int N, int n_out, int top, int scoring) {
+                  int* __restrict__ choice, float* __restrict__ weight, int N, int n_out, int top, int scoring,
+                  float renorm, float wscale) {
     pdl_enter();
     extern __shared__ float route_sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -200,7 +212,7 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ co
         taken[e] = 0.f;
     }
     __syncwarp();
-    route_choose(z, taken, correction, token_seq, choice, weight, n, n_out, top, scoring, lane);
+    route_choose(z, taken, correction, token_seq, choice, weight, n, n_out, top, scoring, lane, renorm, wscale);
 }
 
 // One block.  listed: [cap] pair ids (row * top + choice) expert by expert, -1 where a tile is padded;
@@ -667,7 +679,7 @@ extern "C" int hos_moe_tile_rows() { return kTile; }
 
 extern "C" int hos_moe_route(const void* h, int dtype, const float* router, const float* correction,
                              const int* token_seq, int* choice, float* weight, int N, int D, int n_out, int top,
-                             int scoring, float* logits, cudaStream_t stream) {
+                             int scoring, float* logits, float renorm, float wscale, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (top <= 0 || top > n_out) HOS_REFUSE("moe_route: %d of %d router outputs cannot be chosen", top, n_out);
     // rows to a block: as many as pay (the router matrix is read once per block) and as shared memory holds
@@ -685,7 +697,7 @@ extern "C" int hos_moe_route(const void* h, int dtype, const float* router, cons
     const unsigned groups = logits != nullptr ? (unsigned)((n_out + 7) / 8) : 1u;
 #define HOS_ROUTE(T, RT, VEC)                                                                                        \
     launch_pdl(moe_route_kernel<T, RT, VEC>, dim3(blocks, groups), dim3(256), smem, stream, (const T*)h, router,     \
-               correction, token_seq, choice, weight, N, D, n_out, top, scoring, logits)
+               correction, token_seq, choice, weight, N, D, n_out, top, scoring, logits, renorm, wscale)
 #define HOS_ROUTE_V(T, RT)                                                                                           \
     do {                                                                                                             \
         if (vec) HOS_ROUTE(T, RT, true);                                                                             \
@@ -706,7 +718,7 @@ extern "C" int hos_moe_route(const void* h, int dtype, const float* router, cons
         const size_t csmem = (size_t)4 * 2 * n_out * sizeof(float);
         if (csmem > 48 * 1024) HOS_REFUSE("moe_route: %d router outputs are more than a block's shared memory holds", n_out);
         launch_pdl(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), csmem, stream, (const float*)logits, correction, token_seq,
-                   choice, weight, N, n_out, top, scoring);
+                   choice, weight, N, n_out, top, scoring, renorm, wscale);
     }
     return check_launch("moe_route");
 }

@@ -12,6 +12,8 @@
 //   them staged in shared memory while the chunk before it is walked (cp.async, two buffers).  Columns are
 //   independent of one another in both rules.
 // act_rows: x logistic(x) in place on the leading columns of 32-bit rows (the decay rule's q, k, v).
+// rotate_rows: rotary positions in place on the q and k heads of 32-bit rows (either pairing, the first rot_dims
+//   numbers of a head; angle = position * freq in 32-bit, sincosf), the keys then multiplied by a constant.
 // conv_prep (the delta rule's inputs): per token, the short causal convolution over time of the q, k, v
 //   projections (per channel, `taps` wide, the last tap the current token's, the inputs before a step's first
 //   row from the slot's state), x sigmoid(x) of it, q and k divided by their length per head
@@ -42,6 +44,44 @@ __global__ void act_rows_kernel(float* __restrict__ x, long long ld, int cols, l
     if (i >= n) return;
     float* p = x + (i / cols) * ld + (i % cols);
     *p = silu_precise(*p);
+}
+
+// x: float32 [N][ld]; from column 0 on `Hq` query heads and then `Hk` key heads of `dim` numbers each.  The first
+// rot_dims numbers of every head turn with the token's position: style 0 pairs number i with i + rot_dims / 2,
+// style 1 number 2i with 2i + 1; (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * freq[i].  Every
+// number of a key head is then multiplied by k_mult.  An item is one pair, or one number beyond rot_dims.
+__global__ void __launch_bounds__(256)
+rotate_rows_kernel(float* __restrict__ x, long long ld, int Hq, int Hk, int dim, int rot_dims, int style,
+                   const float* __restrict__ freq, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                   float k_mult) {
+    pdl_enter();
+    extern __shared__ float2 rot_tab[];          // [rot_dims / 2] (sine, cosine) of this token
+    const int n = blockIdx.x;
+    if (token_seq[n] < 0) return;
+    const float fpos = (float)token_pos[n];
+    const int half = rot_dims >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(fpos * freq[i], &sn, &cs);
+        rot_tab[i] = make_float2(sn, cs);
+    }
+    __syncthreads();
+    float* row = x + (size_t)n * ld;
+    const int per = half + (dim - rot_dims);
+    for (int it = threadIdx.x; it < (Hq + Hk) * per; it += blockDim.x) {
+        const int head = it / per, j = it - head * per;
+        const float m = head >= Hq ? k_mult : 1.f;
+        float* hp = row + (size_t)head * dim;
+        if (j < half) {
+            const int a = style == 0 ? j : 2 * j, b = style == 0 ? j + half : 2 * j + 1;
+            const float2 sc = rot_tab[j];
+            const float u = hp[a], v = hp[b];
+            hp[a] = (u * sc.y - v * sc.x) * m;
+            hp[b] = (v * sc.y + u * sc.x) * m;
+        } else if (m != 1.f) {
+            hp[rot_dims + (j - half)] *= m;
+        }
+    }
 }
 
 template <int DR, int R, bool DELTA>
@@ -375,6 +415,22 @@ extern "C" int hos_act_rows(float* x, long long ld, int cols, int N, cudaStream_
     if (n <= 0) return 0;
     launch_pdl(act_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, ld, cols, n);
     return check_launch("act_rows");
+}
+
+// x: float32 rows of ld numbers whose first (Hq + Hk) * dim columns are the query heads and then the key heads; freq:
+// [rot_dims / 2] or null (no rotation: only the keys' multiplier is applied); style 0: halves, 1: neighbours.
+extern "C" int hos_rotate_rows(float* x, long long ld, int Hq, int Hk, int dim, int rot_dims, int style, const float* freq,
+                               const int* token_pos, const int* token_seq, float k_mult, int N, cudaStream_t stream) {
+    if (N <= 0 || Hq + Hk <= 0) return 0;
+    if (freq == nullptr) rot_dims = 0;
+    if (rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > dim) HOS_REFUSE("rotate_rows: %d rotated numbers in heads of %d", rot_dims, dim);
+    if (style != 0 && style != 1) HOS_REFUSE("rotate_rows: unknown pairing %d", style);
+    if (rot_dims == 0 && k_mult == 1.f) return 0;
+    const size_t smem = (size_t)(rot_dims / 2 + 1) * sizeof(float2);
+    if (smem > 48 * 1024) HOS_REFUSE("rotate_rows: %d rotated numbers do not fit", rot_dims);
+    launch_pdl(rotate_rows_kernel, dim3(N), dim3(256), smem, stream, x, ld, Hq, Hk, dim, rot_dims, style, freq, token_pos,
+               token_seq, k_mult);
+    return check_launch("rotate_rows");
 }
 
 // keep_here: 1 only where every sequence of the step brings exactly one token: the kept inputs then move on inside this

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import fobilorn, gemma2, satapel, vagonex  # noqa: F401
+from . import fobilorn, gemma2, satapel, tofodra, vagonex  # noqa: F401

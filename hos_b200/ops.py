@@ -394,6 +394,17 @@ def gated_act(gu: torch.Tensor, out: torch.Tensor, act: int) -> None:
     core().call("hos_gated_act", _ptr(gu), _ptr(out), dtype_code(gu.dtype), n, f, act, _stream())
 
 
+def clamped_gated_act(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+    """out = g logistic(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit) (limit 0: no clamp);
+    gu: float32 [N, 2F] gate then up; out: [N, F] in the products' type."""
+    _check(gu, "gate|up rows", torch.float32, 2)
+    n, f = out.shape
+    if gu.shape != (n, 2 * f):
+        raise KernelError("clamped_gated_act: sizes disagree")
+    core().call("hos_clamped_gated_act", _ptr(gu), _ptr(out), dtype_code(out.dtype), n, f, float(limit), float(alpha),
+                float(shift), _stream())
+
+
 def gather_rows(x: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> None:
     _check(x, "rows", torch.float32, 2)
     _check(idx, "row indices", torch.int32, 1)
@@ -608,16 +619,23 @@ def scaled_add_norms(a: Optional[torch.Tensor], f: Optional[torch.Tensor], mult:
                   dtype_code(h.dtype) if h is not None else 0, n, d, _stream())
 
 
-def latent_prep(proj: torch.Tensor, n_heads: int, dq: int, rank: int, rot: int, w_norm: torch.Tensor, eps: float,
-                inv_freq: Optional[torch.Tensor], rot_dims: int, step, kc: torch.Tensor, q_lat: torch.Tensor,
+def latent_prep(proj: torch.Tensor, n_heads: int, dq: int, rank: int, rot: int, w_norm: Optional[torch.Tensor], eps: float,
+                inv_freq: Optional[torch.Tensor], rot_dims: int, step, kc: Optional[torch.Tensor], q_lat: torch.Tensor,
                 cache: Optional[PagedKVArgs]) -> None:
+    """kc None: the rows hold queries only (a call that reads another call's cache): the queries' rotated parts are
+    written and nothing is normed or stored."""
     _check(proj, "projection rows", None, 2)
-    _check(kc, "latent rows", proj.dtype, 2)
     _check(q_lat, "latent queries", torch.float32, 3)
     n = proj.shape[0]
-    if proj.shape[1] != n_heads * (dq + rot) + rank + rot or kc.shape != (n, rank + rot) \
-            or q_lat.shape != (n, n_heads, rank + rot):
-        raise KernelError("latent_prep: sizes disagree")
+    if kc is None:
+        if proj.shape[1] != n_heads * (dq + rot) or q_lat.shape != (n, n_heads, rank + rot):
+            raise KernelError("latent_prep: sizes disagree")
+        cache = None
+    else:
+        _check(kc, "latent rows", proj.dtype, 2)
+        if proj.shape[1] != n_heads * (dq + rot) + rank + rot or kc.shape != (n, rank + rot) \
+                or q_lat.shape != (n, n_heads, rank + rot) or w_norm is None:
+            raise KernelError("latent_prep: sizes disagree")
     if cache is not None and (cache.k_pages.dtype != proj.dtype or cache.head_dim != rank + rot or cache.n_kv_heads != 1):
         raise KernelError("latent_prep: the cache does not fit the latent rows")
     blocks().call("hos_latent_prep", _ptr(proj), dtype_code(proj.dtype), proj.shape[1], n_heads, dq, rank, rot,
@@ -713,14 +731,18 @@ def moe_tile_rows() -> int:
 MOE_SCORING = {"softmax": 0, "logistic": 1}
 
 
-def moe_route(h, router, correction, token_seq, choice, weight, top: int, scoring: int = 0) -> None:
+def moe_route(h, router, correction, token_seq, choice, weight, top: int, scoring: int = 0,
+              renormalise: Optional[float] = None, weight_scale: float = 1.0) -> None:
+    """renormalise (a number >= 0): the chosen scores are divided by their sum plus that number; weight_scale: a constant
+    on every weight after that."""
     _check(h, "rows", None, 2)
     _check(router, "router", torch.float32, 2)
     n, d = h.shape
     # few rows and many router outputs: the outputs are cut over blocks, which leave their logits here for a second launch
     logits = torch.empty((n, router.shape[0]), dtype=torch.float32, device=h.device) if router.shape[0] > 8 and n < 2048 else None
     experts().call("hos_moe_route", _ptr(h), dtype_code(h.dtype), _ptr(router), _ptr(correction), _ptr(token_seq),
-                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), int(scoring), _ptr(logits), _stream())
+                  _ptr(choice), _ptr(weight), n, d, router.shape[0], int(top), int(scoring), _ptr(logits),
+                  -1.0 if renormalise is None else float(renormalise), float(weight_scale), _stream())
 
 
 def moe_align(choice, n_experts: int, listed, tile_expert) -> None:
@@ -873,15 +895,17 @@ def group_norm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, gate_c
 def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
             eps: float, freq: Optional[torch.Tensor], rot_dims: int, magnitude: float, step, q_out: torch.Tensor,
             cache: PagedKVArgs, n_heads: int, n_kv: int, kd: int, vd: int, norm_whole: bool = False,
-            v_first: Optional[torch.Tensor] = None, v_first_col: int = 0, v_mix: float = 0.0) -> None:
+            v_first: Optional[torch.Tensor] = None, v_first_col: int = 0, v_mix: float = 0.0, q_maps: int = 1) -> None:
     """proj: float32 [N, >= H kd + G (kd + vd)] = [q | k | v | ...] (G = n_kv; 0: a call that stores nothing).  Adds the
     biases, norms and rotates the q and k heads, writes q_out float32 [N, H, kd] and stores k, v in the cache.
     norm_whole: one root mean square over all q heads and one over all k heads (weights [H kd], [G kd]).  v_first
-    (float32 [N, ld], the values from column v_first_col on): v <- (1 - v_mix) v + v_mix v_first before the store."""
+    (float32 [N, ld], the values from column v_first_col on): v <- (1 - v_mix) v + v_mix v_first before the store.
+    q_maps > 1: a head's kd numbers are q_maps queries, one per attention map over the same key row; q_out is then
+    [N, H * q_maps, kd], every query a head of its own that is zero outside its part of the key row."""
     _check(proj, "projection rows", torch.float32, 2)
     _check(q_out, "queries", torch.float32, 3)
     n = proj.shape[0]
-    if q_out.shape != (n, n_heads, kd) or proj.shape[1] < n_heads * kd + n_kv * (kd + vd):
+    if q_out.shape != (n, n_heads * q_maps, kd) or proj.shape[1] < n_heads * kd + n_kv * (kd + vd):
         raise KernelError("qk_prep: sizes disagree")
     if n_kv and (cache.head_dim != kd or cache.v_dim != vd or cache.n_kv_heads != n_kv):
         raise KernelError("qk_prep: the cache does not fit the keys and values")
@@ -898,7 +922,23 @@ def qk_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[t
                   int(rot_dims), float(magnitude), _ptr(step.token_pos), _ptr(step.token_seq), _ptr(step.seq_slot),
                   _ptr(q_out), _ptr(cache.k_pages) if n_kv else None, _ptr(cache.v_pages) if n_kv else None,
                   dtype_code(cache.k_pages.dtype), _ptr(cache.page_table), cache.table_stride, cache.ring_pages, n,
-                  int(n_heads), int(n_kv), int(kd), int(vd), 1 if norm_whole else 0, vf_ptr, vf_ld, float(v_mix), _stream())
+                  int(n_heads), int(n_kv), int(kd), int(vd), 1 if norm_whole else 0, vf_ptr, vf_ld, float(v_mix),
+                  int(q_maps), _stream())
+
+
+def diff_combine(a: torch.Tensor, lam: float, mult: float, eps: float, gate: Optional[torch.Tensor], gate_col: int, step,
+                 out: torch.Tensor, heads: int, vd: int) -> None:
+    """a: float32 [N, heads * 2 * vd], the outputs of a head's two attention maps side by side; out [N, heads * vd] =
+    rms_norm_per_head(a1 - lam a2) * mult * logistic(gate[:, gate_col + column])."""
+    _check(a, "the maps' outputs", torch.float32, 2)
+    n = a.shape[0]
+    if a.shape[1] != heads * 2 * vd or out.shape != (n, heads * vd) or \
+            (gate is not None and (gate.dtype != torch.float32 or gate_col + heads * vd > gate.shape[1])):
+        raise KernelError("diff_combine: sizes disagree")
+    gated_attn_lib().call("hos_diff_combine", _ptr(a), float(lam), float(mult), float(eps),
+                          ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
+                          gate.shape[1] if gate is not None else 0, _ptr(step.token_seq), _ptr(out), dtype_code(out.dtype),
+                          n, int(heads), int(vd), _stream())
 
 
 def gated_attn(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor],
@@ -930,15 +970,17 @@ def gated_attn_mma(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[torch.Ten
     sizes are not that kernel's and nothing ran."""
     n, heads, kd = q.shape
     vd = cache.v_dim
-    if out.dtype != torch.bfloat16 or cache.k_pages.dtype != torch.bfloat16 or out.shape != (n, heads * vd):
+    if out.dtype not in (torch.bfloat16, torch.float32) or cache.k_pages.dtype != torch.bfloat16 \
+            or out.shape != (n, heads * vd):
         return False
-    if kd not in (64, 128) or vd not in (64, 128) or q.data_ptr() % 16 or out.data_ptr() % 4:
+    if kd not in (64, 128) or vd not in (64, 128) or q.data_ptr() % 16 or out.data_ptr() % 8:
         return False
     gated_attn_lib().call("hos_gated_attn_mma", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
                   cache.table_stride, cache.ring_pages, _ptr(sink),
                   ctypes.c_void_p(gate.data_ptr() + gate_col * 4) if gate is not None else None,
                   gate.shape[1] if gate is not None else 0, _ptr(step.cu_seqlens), _ptr(step.token_pos),
-                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), int(step.n_seqs), int(n_q_tiles), heads,
+                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                  int(step.n_seqs), int(n_q_tiles), heads,
                   cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0), _stream())
     return True
 
@@ -950,7 +992,8 @@ def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[to
     sizes are not that kernel's and nothing ran."""
     n, heads, kd = q.shape
     vd = cache.v_dim
-    if out.dtype != torch.bfloat16 or cache.k_pages.dtype != torch.bfloat16 or out.shape != (n, heads * vd):
+    if out.dtype not in (torch.bfloat16, torch.float32) or cache.k_pages.dtype != torch.bfloat16 \
+            or out.shape != (n, heads * vd):
         return False
     if kd not in (64, 128) or vd not in (64, 128) or heads // cache.n_kv_heads > 16 or q.data_ptr() % 16:
         return False
@@ -962,7 +1005,8 @@ def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[to
     gate_ld = gate.shape[1] if gate is not None else 0
     gated_attn_lib().call("hos_gated_attn_mma_decode", _ptr(q), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(cache.page_table),
                   cache.table_stride, cache.ring_pages, _ptr(sink), gate_ptr, gate_ld, _ptr(step.token_pos),
-                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), _ptr(part_acc), _ptr(part_ml), int(n_splits), n,
+                  _ptr(step.token_seq), _ptr(step.seq_slot), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                  _ptr(part_acc), _ptr(part_ml), int(n_splits), n,
                   heads, cache.n_kv_heads, kd, vd, float(scale), int(chunk or 0), int(window or 0), int(keep_first or 0),
                   _stream())
     if n_splits > 1:
@@ -995,6 +1039,23 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
                   _ptr(beta), heads if beta is not None else 0, _ptr(state), _ptr(step.token_pos), _ptr(step.token_seq),
                   _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), n, int(step.n_seqs), int(heads), int(key_heads),
                   int(dim), int(vdim), _stream())
+
+
+def act_rows(rows: torch.Tensor, cols: int) -> None:
+    """x logistic(x), in place, on the first `cols` numbers of float32 rows."""
+    _check(rows, "projection rows", torch.float32, 2)
+    mixers().call("hos_act_rows", _ptr(rows), rows.shape[1], int(cols), rows.shape[0], _stream())
+
+
+def rotate_rows(rows: torch.Tensor, q_heads: int, k_heads: int, dim: int, freq: Optional[torch.Tensor], rot_dims: int,
+                style: int, step, k_mult: float = 1.0) -> None:
+    """Rotary positions, in place, on the leading q_heads + k_heads heads of `dim` numbers of float32 rows (the first
+    rot_dims numbers of each head, pairing `style`), then the key heads times k_mult."""
+    _check(rows, "projection rows", torch.float32, 2)
+    if rows.shape[1] < (q_heads + k_heads) * dim:
+        raise KernelError("rotate_rows: sizes disagree")
+    mixers().call("hos_rotate_rows", _ptr(rows), rows.shape[1], int(q_heads), int(k_heads), int(dim), int(rot_dims),
+                  int(style), _ptr(freq), _ptr(step.token_pos), _ptr(step.token_seq), float(k_mult), rows.shape[0], _stream())
 
 
 def conv_prep(raw: torch.Tensor, conv_w: torch.Tensor, conv_state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,

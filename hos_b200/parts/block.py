@@ -4,6 +4,7 @@ sums are 32-bit.
 
 "sandwich" (Gemma-2, src/forward.rs:291-414): norms before AND after each branch,
     x += post_mixer(mixer(pre_mixer(x)));  x += post_ffn(ffn(pre_ffn(x)))
+    (a layer without a feed-forward has the first line only, and needs the first two norms only).
 "prenorm" (the reference's other families): a norm before each branch only,
     x += mixer(pre_mixer(x));  x += ffn(pre_ffn(x))
 "parallel": both branches read a norm (each its own weight) of the SAME x, and their sum is scaled,
@@ -67,9 +68,17 @@ class Layer:
 
 
 class SandwichLayer(Layer):
-    norm_roles = ("pre_mixer", "post_mixer", "pre_ffn", "post_ffn")
+    norm_roles = ("pre_mixer", "post_mixer")
 
     chains = True
+
+    def __init__(self, spec: LayerSpec, rt: Runtime):
+        super().__init__(spec, rt)
+        from .feedforward import NoFeedForward
+        self.has_ffn = not isinstance(self.feed_forward, NoFeedForward)
+        missing = [r for r in ("pre_ffn", "post_ffn") if self.has_ffn and r not in spec.norms]
+        if missing:
+            raise SpecError(f"arch spec error: arrangement {spec.arrangement!r} needs norms {missing}")
 
     def entry_norm(self):
         return self.norms["pre_mixer"]
@@ -78,6 +87,8 @@ class SandwichLayer(Layer):
         n = self.norms
         h = h_in if h_in is not None else n["pre_mixer"].forward(x)
         a = self._branch(self.mixer, getattr(n["post_mixer"], "accepts_partials", False), h, step, store)
+        if not self.has_ffn:
+            return n["post_mixer"].add_to(a, x, then=next_norm)
         h = n["post_mixer"].add_to(a, x, then=n["pre_ffn"])     # x += post(a); h = pre_ffn(x)
         f = self._branch(self.feed_forward, getattr(n["post_ffn"], "accepts_partials", False), h, step)
         return n["post_ffn"].add_to(f, x, then=next_norm)       # x += post(f); next layer's entry norm

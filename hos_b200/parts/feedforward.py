@@ -2,7 +2,12 @@
 activation as a parameter ("gelu_tanh" is Gemma's GeGLU, src/forward.rs:186-189;
 "silu" is the reference's other branch, :393).  Gate and up are one product whose
 epilogue applies the activation and the product, so the 2*inner-wide intermediate
-is never written."""
+is never written.
+
+"clamped_swish" is the form g = min(gate(h), limit), u = clamp(up(h), -limit, limit), down(g logistic(alpha g)
+(u + up_shift)) with `limit`, `alpha` (1.702 by default) and `up_shift` (1 by default) as parameters: the form the
+routed experts' kernels know, for a dense layer.  Gate and up come out of one product as 32-bit rows; the clamp, the
+activation and the product are 32-bit and rounded once."""
 from __future__ import annotations
 
 from typing import List, Mapping
@@ -24,9 +29,12 @@ class GatedMLP(FeedForward):
         self.width = int(spec.params["width"])
         self.inner = int(spec.params["inner"])
         act = spec.params.get("activation", "gelu_tanh")
-        if act not in ops.ACTIVATIONS:
+        self.clamped = act == "clamped_swish"
+        if not self.clamped and act not in ops.ACTIVATIONS:
             raise SpecError(f"arch spec error: unknown activation {act!r}")
-        self.act = ops.ACTIVATIONS[act]
+        self.act = 0 if self.clamped else ops.ACTIVATIONS[act]
+        self.limit = float(spec.params.get("limit") or 0.0)
+        self.alpha, self.up_shift = float(spec.params.get("alpha", 1.702)), float(spec.params.get("up_shift", 1.0))
         self.w_gate_up = self.w_down = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -43,15 +51,21 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()    # gate rows, then up rows
         self.w_down = self._matrix(tensors[w["down"]])
 
+    def _inner(self, h: torch.Tensor) -> torch.Tensor:
+        if not self.clamped:
+            return linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
+        gu = linear.matmul(h, self.w_gate_up, out_dtype=torch.float32)
+        z = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+        ops.clamped_gated_act(gu, z, self.limit, self.alpha, self.up_shift)
+        return z
+
     def forward(self, h: torch.Tensor, step: StepInfo = None) -> torch.Tensor:
-        z = linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
-        return linear.matmul(z, self.w_down)
+        return linear.matmul(self._inner(h), self.w_down)
 
     def forward_partial(self, h: torch.Tensor, step: StepInfo = None) -> torch.Tensor:
         """As forward, but the down projection may come back as float32 partial sums
         [parts, N, width] for a consumer that adds them."""
-        z = linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
-        return linear.matmul_or_partials(z, self.w_down)
+        return linear.matmul_or_partials(self._inner(h), self.w_down)
 
 
 class NoFeedForward(FeedForward):

@@ -16,6 +16,11 @@ tensor cores with every 32-bit operand as two bfloat16 terms (csrc/latent_attent
 Cache: one keys-only group of row size kv_rank + rot_dim, a window ring if `window` is set.
 A sequence that starts at position 0 attends over the step's own rows; one that goes on (by
 one token or many) stores first and attends over the cache.
+
+A call that reads another call's cache (`shares_kv`) has no down projection and no latent norm: it projects
+and rotates its own queries and attends, with its own W_uk and W_uv, over the rows that the other call has
+stored (this step's rows among them), every row over the cache.  The other call's kv_rank, rot_dim and
+rotation are this one's.
 """
 from __future__ import annotations
 
@@ -49,6 +54,9 @@ class LatentAttention(Mixer):
         self.eps = float(p["eps"])
         self.window: Optional[int] = p.get("window")
         self.has_sink = bool(p.get("sink", False))
+        self.shares_kv = bool(p.get("shares_kv", False))
+        if self.shares_kv and self.window:
+            raise SpecError("arch spec error: a latent attention that reads another call's cache keeps no window of its own")
         pos_spec = p.get("position")
         self.position = part_impl("position", pos_spec.kind)(pos_spec, rt) if pos_spec else None
         if min(self.n_heads, self.dim, self.rot_dim, self.vdim, self.rank) <= 0:
@@ -58,10 +66,11 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> List[WeightSpec]:
         w = self.spec.weights
-        out = [WeightSpec(w["q"], (self.q_cols, self.width), "matrix", 0.02),
-               WeightSpec(w["dkv"], (self.row, self.width), "matrix", 0.02),
-               WeightSpec(w["dkv_norm"], (self.rank,), "vector", 0.1),
-               WeightSpec(w["uk"], (self.n_heads * self.dim, self.rank), "matrix", 0.05),
+        out = [WeightSpec(w["q"], (self.q_cols, self.width), "matrix", 0.02)]
+        if not self.shares_kv:
+            out += [WeightSpec(w["dkv"], (self.row, self.width), "matrix", 0.02),
+                    WeightSpec(w["dkv_norm"], (self.rank,), "vector", 0.1)]
+        out += [WeightSpec(w["uk"], (self.n_heads * self.dim, self.rank), "matrix", 0.05),
                WeightSpec(w["uv"], (self.n_heads * self.vdim, self.rank), "matrix", 0.05),
                WeightSpec(w["o"], (self.width, self.n_heads * self.vdim), "matrix", 0.02)]
         if self.has_sink:
@@ -70,11 +79,15 @@ class LatentAttention(Mixer):
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         w = self.spec.weights
-        q, dkv = self._matrix(tensors[w["q"]]), self._matrix(tensors[w["dkv"]])
-        if q.dtype != dkv.dtype:
-            q, dkv = q.float(), dkv.float()
-        self.w_in = torch.cat([q, dkv], dim=0).contiguous()          # one product for q and the down projection
-        self.w_norm = self._vector32(tensors[w["dkv_norm"]])
+        q = self._matrix(tensors[w["q"]])
+        if self.shares_kv:
+            self.w_in, self.w_norm = q, None
+        else:
+            dkv = self._matrix(tensors[w["dkv"]])
+            if q.dtype != dkv.dtype:
+                q, dkv = q.float(), dkv.float()
+            self.w_in = torch.cat([q, dkv], dim=0).contiguous()          # one product for q and the down projection
+            self.w_norm = self._vector32(tensors[w["dkv_norm"]])
         uk = self._matrix(tensors[w["uk"]]).view(self.n_heads, self.dim, self.rank)
         self.w_uk_t = uk.transpose(1, 2).contiguous()                # [heads, rank, dim]: q'_h = W_uk_h^T q_h
         self.w_uv = self._matrix(tensors[w["uv"]]).view(self.n_heads, self.vdim, self.rank).contiguous()
@@ -100,11 +113,12 @@ class LatentAttention(Mixer):
     def forward(self, h: torch.Tensor, step: StepInfo, store: CallStore) -> torch.Tensor:
         n = h.shape[0]
         cache = store.kv
-        if cache is None or not store.owns_kv:
-            raise KernelError("latent attention needs a cache of its own")
+        if cache is None or store.owns_kv == self.shares_kv:
+            raise KernelError("latent attention: the call's cache and the mixer's tensors do not fit (a mixer without a "
+                              "down projection reads another call's cache, and only such a mixer does)")
         H, R, D = self.n_heads, self.rank, self.row
         proj = linear.matmul(h, self.w_in)
-        kc = torch.empty((n, D), dtype=h.dtype, device=h.device)
+        kc = None if self.shares_kv else torch.empty((n, D), dtype=h.dtype, device=h.device)
         q_lat = torch.empty((n, H, D), dtype=torch.float32, device=h.device)
         inv_freq, rot_dims, style = self.position.kernel_args() if self.position else (None, 0, 1)
         if inv_freq is not None and style != ops.ROPE_STYLES["interleaved"]:
@@ -113,7 +127,7 @@ class LatentAttention(Mixer):
         # q'_h = W_uk_h^T q_h into the first `rank` numbers of every head's latent query
         ops.heads_product(proj, 0, proj.shape[1], self.dim + self.rot_dim, self.w_uk_t, q_lat, 0, H * D, D, n)
         o_lat = torch.empty((n, H, R), dtype=h.dtype, device=h.device)      # what the value expansion reads
-        nf = n if step.from_zero else step.fresh_tokens
+        nf = 0 if self.shares_kv else (n if step.from_zero else step.fresh_tokens)
         if nf > 0:
             shares, per_block = self.plan(nf, step)
             ops.latent_attn(q_lat, kc, None, self.sink, o_lat, step, 0, nf, R, self.scale, self.window, paged=False,

@@ -4,7 +4,8 @@ Router logits z = W_router h in 32-bit; scores s = softmax(z) over all router ou
 "softmax") or the logistic function of each logit alone ("logistic").  The `top` outputs with the largest
 s + correction are chosen (the correction, if the model has one, only steers the choice); each chosen
 expert is weighted by its plain score s, not renormalised: its output is (`weight_on` "output"), or its
-input, expert(s h) ("input").  The last `identity` router outputs are experts without tensors whose
+input, expert(s h) ("input").  With `renormalise` (a number >= 0) the chosen scores are first divided by their sum
+plus that number, and `weight_scale` is a constant on every weight after that.  The last `identity` router outputs are experts without tensors whose
 output is the row itself.
 Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift),
 output W_down y; no biases (`up_shift` 1 and `alpha` 1.702 by default; 0 and 1 make the plain gated form
@@ -43,6 +44,10 @@ class RoutedExperts(FeedForward):
         if scoring not in ops.MOE_SCORING or weight_on not in ("output", "input"):
             raise SpecError(f"arch spec error: routed experts with scoring {scoring!r} and the weight on {weight_on!r}")
         self.scoring, self.weight_on_input = ops.MOE_SCORING[scoring], weight_on == "input"
+        self.renormalise = p.get("renormalise")            # None, or the number added to the chosen scores' sum
+        self.weight_scale = float(p.get("weight_scale", 1.0))
+        if self.renormalise is not None and float(self.renormalise) < 0.0:
+            raise SpecError("arch spec error: the number added to the chosen scores' sum cannot be negative")
         shared = p.get("shared")
         self.shared = part_impl("feed_forward", shared.kind)(shared, rt) if shared is not None else None
         if self.n_experts < 0 or self.n_identity < 0 or not 0 < self.top <= self.n_experts + self.n_identity:
@@ -84,7 +89,8 @@ class RoutedExperts(FeedForward):
         pairs = n * top
         choice = torch.empty(pairs, dtype=torch.int32, device=dev)
         weight = torch.empty(pairs, dtype=torch.float32, device=dev)
-        ops.moe_route(h, self.router, self.correction, step.token_seq, choice, weight, top, self.scoring)
+        ops.moe_route(h, self.router, self.correction, step.token_seq, choice, weight, top, self.scoring,
+                      self.renormalise, self.weight_scale)
         out = torch.empty((n, self.width), dtype=torch.float32, device=dev)
         pair_out = None
         if self.n_experts > 0:

@@ -1,5 +1,8 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * (w + add_one)  (src/forward.rs:166-174;
-`add_one` is Gemma's (1 + w) convention, src/hf.rs:101-107).  Statistics in 32-bit."""
+`add_one` is Gemma's (1 + w) convention, src/hf.rs:101-107).  Statistics in 32-bit.
+A norm may name a second tensor, `scale`: a multiplier per column on the norm's output (the layer scale of a
+branch whose last act is this norm).  It is folded into the weight when the tensors are bound, (w + add_one) * scale
+in 32-bit, which is exact for weights stored in bfloat16 (16 bits of product) and one rounding otherwise."""
 from __future__ import annotations
 
 from typing import List, Mapping, Optional
@@ -22,10 +25,17 @@ class RMSNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", 0.1)]
+        out = [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", 0.1)]
+        if self.spec.weights.get("scale"):
+            out.append(WeightSpec(self.spec.weights["scale"], (self.width,), "vector", 0.1))
+        return out
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = self._vector32(tensors[self.spec.weights["weight"]])
+        if self.spec.weights.get("scale"):
+            # y * w * scale == y * (w * scale); with Gemma's convention the kernel adds one, so that is taken here
+            scale = self._vector32(tensors[self.spec.weights["scale"]])
+            self.weight = ((self.weight + 1.0) * scale - 1.0 if self.add_one else self.weight * scale).contiguous()
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if out is None:

@@ -3,7 +3,10 @@
 decay_linear_attention: q, k = act(W_q h), act(W_k h) (heads x dim), v = act(W_v h) (heads x vdim), act(x) = x
     logistic(x); per head S <- decay_h S + k v^T, o = S^T q with a constant decay per head and no other scale; the
     heads' outputs, side by side, are divided by their common root mean square, multiplied by a weight per column
-    and by logistic(W_g h), and projected by W_o.
+    and by logistic(W_g h), and projected by W_o.  Each piece is a parameter: `activation` ("x_logistic", or None for
+    q, k, v as projected); `position` (a rotary part: q and k turn with the token's position after the activation,
+    angles in 32-bit); `key_scale` (a constant on k after the rotation); `norm` ("row": one root mean square over all
+    heads; "head": one per head) with or without a weight (`norm_weight`); `gate` ("logistic" or "x_logistic").
 gated_delta_rule: q, k (kv_heads x dim) and v (heads x vdim) each pass a short causal convolution over time per
     channel (`taps` wide, zeros before a sequence's start) and x logistic(x); q and k are divided by their lengths
     (sqrt(sum + 1e-6)) per head, q also by sqrt(dim); beta = logistic(W_b h) and the decay
@@ -24,7 +27,7 @@ import torch
 
 from .. import ops
 from ..errors import SpecError
-from ..registry import register_part
+from ..registry import part_impl, register_part
 from . import linear
 from .base import CallStore, Mixer, StateNeed, StepInfo, WeightSpec
 
@@ -41,15 +44,26 @@ class DecayLinearAttention(Mixer):
         if min(self.width, self.n_heads, self.dim, self.vdim) <= 0 or len(self.decay) != self.n_heads:
             raise SpecError("arch spec error: the decay mixer needs positive sizes and one decay per head")
         self.qk_cols, self.v_cols = self.n_heads * self.dim, self.n_heads * self.vdim
+        act, norm, gate = p.get("activation", "x_logistic"), p.get("norm", "row"), p.get("gate", "logistic")
+        if act not in (None, "x_logistic") or norm not in ("row", "head") or gate not in ("logistic", "x_logistic"):
+            raise SpecError(f"arch spec error: the decay mixer with activation {act!r}, norm {norm!r}, gate {gate!r}")
+        self.activates, self.norm_per_head = act is not None, norm == "head"
+        self.norm_weight = bool(p.get("norm_weight", True))
+        self.gate_act = ops.ACT_X_LOGISTIC if gate == "x_logistic" else ops.ACT_LOGISTIC
+        self.key_scale = float(p.get("key_scale", 1.0))
+        pos_spec = p.get("position")
+        self.position = part_impl("position", pos_spec.kind)(pos_spec, rt) if pos_spec else None
 
     def weight_specs(self) -> List[WeightSpec]:
         w = self.spec.weights
-        return [WeightSpec(w["q"], (self.qk_cols, self.width), "matrix", 0.05),
-                WeightSpec(w["k"], (self.qk_cols, self.width), "matrix", 0.05),
-                WeightSpec(w["v"], (self.v_cols, self.width), "matrix", 0.05),
-                WeightSpec(w["gate"], (self.v_cols, self.width), "matrix", 0.05),
-                WeightSpec(w["norm"], (self.v_cols,), "vector", 0.1),
-                WeightSpec(w["o"], (self.width, self.v_cols), "matrix", 0.02)]
+        out = [WeightSpec(w["q"], (self.qk_cols, self.width), "matrix", 0.05),
+               WeightSpec(w["k"], (self.qk_cols, self.width), "matrix", 0.05),
+               WeightSpec(w["v"], (self.v_cols, self.width), "matrix", 0.05),
+               WeightSpec(w["gate"], (self.v_cols, self.width), "matrix", 0.05),
+               WeightSpec(w["o"], (self.width, self.v_cols), "matrix", 0.02)]
+        if self.norm_weight:       # a weight per column, or one shared by the heads where the norm is per head
+            out.append(WeightSpec(w["norm"], (self.vdim if self.norm_per_head else self.v_cols,), "vector", 0.1))
+        return out
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         w = self.spec.weights
@@ -57,8 +71,12 @@ class DecayLinearAttention(Mixer):
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
         self.w_in = torch.cat(mats, dim=0).contiguous()
-        self.norm_w = self._vector32(tensors[w["norm"]])
         self.w_o = self._matrix(tensors[w["o"]])
+        if self.norm_weight:
+            self.norm_w = self._vector32(tensors[w["norm"]])
+        else:
+            self.norm_w = torch.ones(self.vdim if self.norm_per_head else self.v_cols, dtype=torch.float32,
+                                     device=self.w_o.device)
         self.decay_t = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(self.w_o.device)
 
     def state_needs(self) -> List[StateNeed]:
@@ -74,11 +92,22 @@ class DecayLinearAttention(Mixer):
         n = h.shape[0]
         proj = linear.matmul(h, self.w_in, out_dtype=torch.float32)
         o = torch.empty((n, self.v_cols), dtype=torch.float32, device=h.device)
-        ops.state_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, True, self.decay_t, False, None, store.state["S"], step, o,
-                       self.n_heads, self.n_heads, self.dim, self.vdim)
+        turns = self.position is not None or self.key_scale != 1.0
+        if turns:
+            # the rotation follows the activation, so the activation cannot ride in the scan's walk here
+            if self.activates:
+                ops.act_rows(proj, 2 * self.qk_cols + self.v_cols)
+            freq, rot_dims, style = self.position.kernel_args() if self.position else (None, 0, 0)
+            ops.rotate_rows(proj, self.n_heads, self.n_heads, self.dim, freq, rot_dims, style, step, self.key_scale)
+        ops.state_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, self.activates and not turns, self.decay_t, False, None,
+                       store.state["S"], step, o, self.n_heads, self.n_heads, self.dim, self.vdim)
         y = torch.empty((n, self.v_cols), dtype=h.dtype, device=h.device)
-        ops.group_norm_gate(o, self.norm_w, proj, 2 * self.qk_cols + self.v_cols, ops.ACT_LOGISTIC, step.token_seq, y,
-                            self.eps, 1, self.v_cols)
+        if self.norm_per_head:
+            ops.group_norm_gate(o, self.norm_w, proj, 2 * self.qk_cols + self.v_cols, self.gate_act, step.token_seq, y,
+                                self.eps, self.n_heads, self.vdim)
+        else:
+            ops.group_norm_gate(o, self.norm_w, proj, 2 * self.qk_cols + self.v_cols, self.gate_act, step.token_seq, y,
+                                self.eps, 1, self.v_cols)
         return linear.matmul_or_partials(y, self.w_o) if partial_ok else linear.matmul(y, self.w_o)
 
 
