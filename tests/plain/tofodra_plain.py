@@ -72,7 +72,8 @@ def latent_rows(m, eps, w, p, h):
 
 
 def latent_mixer(m, eps, w, p, h, rows):
-    """`rows` = (c, kr) of this layer or of the layer it reads."""
+    """`rows` = (c, kr) of this layer or of the layer it reads.  The design's latent layers see every earlier key; a
+    test may name a mask in the constants to take keys away."""
     T, H, d, r, vd = h.shape[0], m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     c, kr = rows
     q = (h @ w[p + "q"].T).view(T, H, d + r)
@@ -82,9 +83,10 @@ def latent_mixer(m, eps, w, p, h, rows):
     for i in range(T):
         for hd in range(H):
             qr = rotate_pairs(q[i, hd, d:], i, m["rot"])
-            s = (k[:i + 1, hd] @ q[i, hd, :d] + kr[:i + 1] @ qr) * m["scale"]
+            js = torch.tensor([j for j in range(T) if visible(i, j, m.get("mask"))])
+            s = (k[js, hd] @ q[i, hd, :d] + kr[js] @ qr) * m["scale"]
             pr = torch.softmax(s, 0)
-            out[i, hd] = pr @ v[:i + 1, hd]
+            out[i, hd] = pr @ v[js, hd]
     return out.reshape(T, H * vd) @ w[p + "o"].T
 
 
@@ -97,8 +99,10 @@ def retention_mixer(m, eps, w, p, h):
     for hd in range(H):
         S = torch.zeros(d, vd, dtype=h.dtype)
         for t in range(T):
-            qt = rotate_halves(q[t, hd], t, m["rot"])
-            kt = rotate_halves(k[t, hd], t, m["rot"]) * d ** -0.5
+            qt, kt = q[t, hd], k[t, hd]
+            if m.get("rot"):            # a layer whose constants name no rotation turns nothing
+                qt, kt = rotate_halves(qt, t, m["rot"]), rotate_halves(kt, t, m["rot"])
+            kt = kt * d ** -0.5
             S = m["decay"][hd] * S + torch.outer(kt, v[t, hd])
             out[t, hd] = rms(S.T @ qt, eps)
     return (out.reshape(T, H * vd) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
@@ -140,7 +144,7 @@ def expert_ff(w, p, h):
 
 
 def routed_ff(mlp, w, p, h):
-    n, top, mult = mlp["router"]["experts"], mlp["router"]["top"], mlp["router"]["scale"]
+    n, top, mult = mlp["router"]["experts"], mlp["router"]["top"], mlp["router"].get("scale", 1.0)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         s = torch.sigmoid(h[t] @ w[p + "router"].T)
