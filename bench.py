@@ -12,7 +12,7 @@ back to the host, where the loop reads them one step late.  `prefill` is one pro
 step must read (every weight once, and the cache of the live sequences) to its time.
 `points` holds decoding at batch 1 and 64.  One JSON line is printed.
 
-`--design satapel` (or `vagonex`, `fobilorn`) is another measurement (not the line above): prompt and decode throughput of that design at
+`--design satapel` (or `vagonex`, `fobilorn`, `tofodra`) is another measurement (not the line above): prompt and decode throughput of that design at
 a few sizes beside Gemma-2 at equal size, and each of the design's kernels against its roofline; one JSON line per size.
 With `--profile prefill|decode` it measures nothing and runs two such steps of one block of layers kernel by kernel, for a profiler.
 
@@ -472,11 +472,141 @@ def fobilorn_kernel_work(z, tokens, batch, ctx):
     }
 
 
+# ---- --design tofodra: the Tofodra design beside Vagonex at equal size -----------------------------------
+# Layers in the order (latent attention, retention, differential attention, latent attention that reads the first one's
+# cache) x blocks; dense clamped feed-forwards on the first and third of a block, routed experts with a shared one on
+# the others.  The closest existing model is Vagonex (layers listed one by one, a decay-rule matrix state, attention
+# through the same grouped-query kernels, a layer that reads another layer's cache, a dense gated feed-forward):
+# "Vagonex at equal size" has the same width, layer count and vocabulary, a decay-rule layer where Tofodra has retention
+# (same heads), attention of as many heads over as many kv heads with keys as wide as both maps together where Tofodra
+# has any attention (chunks as long as the window; the fourth layer of a block reads the third's cache), and a dense
+# feed-forward as wide as what a Tofodra token uses on average.
+TOFODRA_SIZES = {
+    "s": dict(width=1024, vocab=32000, blocks=2, lat_heads=8, lat_dim=64, lat_rot=32, lat_vdim=64, rank=256,
+              ret_heads=8, ret_dim=128, ret_vdim=128, heads=8, kv_heads=2, dim=64, vdim=128, window=1024, keep=4,
+              dense_ff=4096, experts=8, top=2, ff=1024, shared=2048),
+    "m": dict(width=2048, vocab=32000, blocks=2, lat_heads=16, lat_dim=64, lat_rot=64, lat_vdim=128, rank=512,
+              ret_heads=16, ret_dim=128, ret_vdim=128, heads=16, kv_heads=4, dim=64, vdim=128, window=1024, keep=4,
+              dense_ff=8192, experts=16, top=2, ff=1536, shared=3072),
+    "l": dict(width=4096, vocab=64000, blocks=1, lat_heads=32, lat_dim=64, lat_rot=64, lat_vdim=128, rank=512,
+              ret_heads=32, ret_dim=128, ret_vdim=128, heads=32, kv_heads=8, dim=64, vdim=128, window=2048, keep=4,
+              dense_ff=14336, experts=32, top=4, ff=1024, shared=4096),
+}
+
+
+def tofodra_raw(z):
+    dense = {"kind": "dense", "ff": z["dense_ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5},
+           "shared": {"ff": z["shared"]}}
+    lat = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["lat_rot"], "vdim": z["lat_vdim"], "kv_rank": z["rank"],
+           "scale": (z["lat_dim"] + z["lat_rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["lat_rot"]}}
+    ret = {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_vdim"], "rot": {"base": 10000.0, "dims": z["ret_dim"]},
+           "decay": [1.0 - 2.0 ** -(5 + 5 * i / max(1, z["ret_heads"] - 1)) for i in range(z["ret_heads"])]}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+           "diff": 0.6, "mask": {"size": z["window"], "keep_first": z["keep"]}}
+    layers = []
+    for b in range(z["blocks"]):
+        layers += [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "retention", "mixer": ret, "mlp": moe},
+                   {"type": "attention", "mixer": att, "mlp": dense},
+                   {"type": "latent_attention", "mixer": dict(lat, kv_from=4 * b), "mlp": moe}]
+    return {"architecture": "Tofodra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": layers}
+
+
+def vagonex_raw_like_tofodra(z):
+    used = (z["dense_ff"] + z["top"] * z["ff"] + z["shared"]) // 2 // 64 * 64      # what a token uses, averaged over a block
+    mlp = {"kind": "dense", "ff": used}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 2 * z["dim"], "vdim": z["vdim"], "scale": (2 * z["dim"]) ** -0.5,
+           "mask": {"size": z["window"]}, "rot": {"base": 10000.0, "dims": z["dim"]}}
+    dec = {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_vdim"],
+           "decay": [1.0 - 2.0 ** -(5 + 5 * i / max(1, z["ret_heads"] - 1)) for i in range(z["ret_heads"])]}
+    layers = []
+    for b in range(z["blocks"]):
+        layers += [{"type": "attention", "mixer": att, "mlp": mlp}, {"type": "lightning", "mixer": dec, "mlp": mlp},
+                   {"type": "attention", "mixer": att, "mlp": mlp},
+                   {"type": "attention", "mixer": dict(att, kv_from=4 * b + 2), "mlp": mlp}]
+    return {"architecture": "Vagonex", "vocab": z["vocab"], "width": z["width"], "postln_alpha": 2.0, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": layers}
+
+
+def tofodra_kernel_work(z, tokens, batch, ctx):
+    """Per launch of each of the design's own kernels: (bytes that must move, FLOPs of the mathematics) for a prompt of
+    `tokens` tokens and for a decode step of `batch` sequences at length `ctx` (bfloat16 cache and products, 32-bit rows
+    and states).  The differential attention's mathematics counts both maps' scores over `dim` numbers each; the kernel
+    issues them over key rows of 2 x dim."""
+    LH, D, R = z["lat_heads"], z["rank"] + z["lat_rot"], z["rank"]
+    all_pairs = tokens * (tokens + 1) // 2
+    H, G, d, vd, W, K = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["window"], z["keep"]
+    kd = 2 * d
+    seen = lambda p: min(p + 1, W) + min(K, max(0, p + 1 - W))        # keys position p sees
+    pairs, keys = sum(seen(p) for p in range(tokens)), seen(ctx - 1)
+    sh, sd, sv = z["ret_heads"], z["ret_dim"], z["ret_vdim"]
+    top, ff, width, E = z["top"], z["ff"], z["width"], z["experts"]
+    touched = min(E, batch * top)
+    maps = {"prefill": (tokens * G * (kd + vd) * 2 + tokens * 2 * H * (kd * 4 + vd * 4), 2.0 * pairs * 2 * H * (d + vd)),
+            "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * 2 * H * (d + vd))}
+
+    def scan(n, seqs):        # q, k, v rows in, o rows out, the state in and out; the update and the read-out: 4 per cell
+        return n * (2 * sh * sd + 2 * sh * sv) * 4 + seqs * sh * sd * sv * 4 * 2, 4.0 * n * sh * sd * sv
+    return {
+        "hos_latent_attn": {"prefill": (tokens * D * 2 + tokens * LH * (D + R) * 4, 2.0 * all_pairs * LH * (D + R)),
+                            "decode": (batch * ctx * D * 2, 2.0 * batch * ctx * LH * (D + R))},
+        "hos_heads_product": {"prefill": (0, 2.0 * tokens * LH * R * (z["lat_dim"] + z["lat_vdim"]) / 2),
+                              "decode": (LH * R * (z["lat_dim"] + z["lat_vdim"]) * 2 / 2,
+                                         2.0 * batch * LH * R * (z["lat_dim"] + z["lat_vdim"]) / 2)},
+        "hos_state_scan": {"prefill": scan(tokens, 1), "decode": scan(batch, batch)},
+        # q and k rows read and written in place (32-bit)
+        "hos_rotate_rows": {"prefill": (tokens * 2 * sh * sd * 8, 0.0), "decode": (batch * 2 * sh * sd * 8, 0.0)},
+        "hos_group_norm_gate": {"prefill": (tokens * sh * sv * 10, 0.0), "decode": (batch * sh * sv * 10, 0.0)},
+        "hos_gated_attn": maps, "hos_gated_attn_mma": maps, "hos_gated_attn_mma_decode": maps,
+        # the fused row in (32-bit), the padded queries out (32-bit, both maps), keys and values out
+        "hos_qk_prep": {"prefill": (tokens * (H * kd * 4 + 2 * H * kd * 4 + G * (kd + vd) * 6), 0.0),
+                        "decode": (batch * (H * kd * 4 + 2 * H * kd * 4 + G * (kd + vd) * 6), 0.0)},
+        # both maps' outputs and the gate logits in (32-bit), the gated heads out
+        "hos_diff_combine": {"prefill": (tokens * H * vd * (8 + 4 + 2), 0.0), "decode": (batch * H * vd * (8 + 4 + 2), 0.0)},
+        "hos_clamped_gated_act": {"prefill": (tokens * z["dense_ff"] * (8 + 2), 0.0), "decode": (batch * z["dense_ff"] * (8 + 2), 0.0)},
+        # x in and out (32-bit), the branch's output in, the normed rows out
+        "hos_norm_add_norm": {"prefill": (tokens * width * 12, 0.0), "decode": (batch * width * 12, 0.0)},
+        "hos_moe_gate_up": {"prefill": (E * 2 * ff * width * 2, 4.0 * tokens * top * ff * width),
+                            "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * ff * width)},
+        "hos_moe_down": {"prefill": (E * ff * width * 2, 2.0 * tokens * top * ff * width),
+                         "decode": (touched * ff * width * 2, 2.0 * batch * top * ff * width)},
+        "hos_moe_gate_up_few": {"prefill": (0, 0.0), "decode": (touched * 2 * ff * width * 2, 4.0 * batch * top * ff * width)},
+        "hos_moe_down_few": {"prefill": (0, 0.0), "decode": (touched * ff * width * 2, 2.0 * batch * top * ff * width)},
+        "hos_moe_combine": {"prefill": (tokens * width * (4 * top + 2 + 4), 0.0), "decode": (batch * width * (4 * top + 2 + 4), 0.0)},
+    }
+
+
 DESIGNS = {"fobilorn": lambda: (FOBILORN_SIZES, fobilorn_raw, gemma_raw_like_fobilorn, fobilorn_kernel_work,
                                 ("hos_gated_attn",)),
            "satapel": lambda: (SATAPEL_SIZES, satapel_raw, gemma_raw_like, satapel_kernel_work, ("hos_wkv_scan",)),
            "vagonex": lambda: (VAGONEX_SIZES, vagonex_raw, gemma_raw_like_vagonex, vagonex_kernel_work,
+                               ("hos_state_scan", "hos_gated_attn")),
+           "tofodra": lambda: (TOFODRA_SIZES, tofodra_raw, vagonex_raw_like_tofodra, tofodra_kernel_work,
                                ("hos_state_scan", "hos_gated_attn"))}
+
+
+def _vagonex_work_like_tofodra(z, tokens, batch, ctx):
+    """The compared model's kernels at the equal-size configuration: attention over keys of 2 x dim numbers in chunks as
+    long as the window, the decay-rule scan of as many heads."""
+    H, G, kd, vd, C = z["heads"], z["kv_heads"], 2 * z["dim"], z["vdim"], z["window"]
+    pairs, keys = sum(p % C + 1 for p in range(tokens)), (ctx - 1) % C + 1
+    sh, sd, sv = z["ret_heads"], z["ret_dim"], z["ret_vdim"]
+    attn = {"prefill": (tokens * G * (kd + vd) * 2 + tokens * H * (kd * 4 + vd * 2), 2.0 * pairs * H * (kd + vd)),
+            "decode": (batch * keys * G * (kd + vd) * 2, 2.0 * batch * keys * H * (kd + vd))}
+
+    def scan(n, seqs):
+        return n * (2 * sh * sd + 2 * sh * sv) * 4 + seqs * sh * sd * sv * 4 * 2, 4.0 * n * sh * sd * sv
+    return {"hos_gated_attn": attn, "hos_gated_attn_mma": attn, "hos_gated_attn_mma_decode": attn,
+            "hos_state_scan": {"prefill": scan(tokens, 1), "decode": scan(batch, batch)},
+            "hos_qk_prep": {"prefill": (tokens * (H * kd * 8 + G * (kd + vd) * 6), 0.0),
+                            "decode": (batch * (H * kd * 8 + G * (kd + vd) * 6), 0.0)},
+            "hos_group_norm_gate": {"prefill": (tokens * sh * sv * 10, 0.0), "decode": (batch * sh * sv * 10, 0.0)},
+            "hos_scale_add_norm": {"prefill": (tokens * z["width"] * 12, 0.0), "decode": (batch * z["width"] * 12, 0.0)}}
+
+
+OTHER_WORK = {"tofodra": _vagonex_work_like_tofodra}
+OTHER_ARM = {"tofodra": "vagonex_equal_size"}      # the closest existing model per design (Gemma-2 where none is named)
 
 
 def run_design_profile_step(args) -> int:
@@ -489,6 +619,8 @@ def run_design_profile_step(args) -> int:
     from hos_b200.registry import config_from_dict
     sizes, raw_of, _, _, _ = DESIGNS[args.design]()
     z = dict(sizes[args.sizes.split(",")[0]], blocks=1)
+    if args.arm == "other":
+        raw_of = DESIGNS[args.design]()[2]
     if "layers" in z:
         z["layers"] = min(4, z["layers"])
     b = int(args.batches.split(",")[-1])
@@ -532,7 +664,7 @@ def run_design_comparison(args) -> int:
         z = sizes[name]
         line = {"design": args.design, "size": name, "sizes": z, "prompt_tokens": tokens, "decode_ctx": ctx, "peaks": pk_src,
                 "dtype": "bf16", "data": "synthetic (random weights)"}
-        for which, raw in ((args.design, raw_of(z)), ("gemma2_equal_size", gemma_of(z))):
+        for which, raw in ((args.design, raw_of(z)), (OTHER_ARM.get(args.design, "gemma2_equal_size"), gemma_of(z))):
             cfg = config_from_dict(raw)
             batches = [int(b) for b in args.batches.split(",")]
             eng = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_batch=max(batches),
@@ -575,7 +707,8 @@ def run_design_comparison(args) -> int:
                 ops.time_calls(False)
                 for s in slots:
                     r.release(s)
-                work = work_of(z, tokens, b, ctx) if which == args.design else {}
+                work = work_of(z, tokens, b, ctx) if which == args.design else \
+                    (OTHER_WORK[args.design](z, tokens, b, ctx) if args.design in OTHER_WORK else {})
                 rows = {}
                 for fn, (n, ms) in sorted(times.items(), key=lambda kv: -kv[1][1]):
                     row = {"calls": n, "ms": round(ms, 4)}
@@ -626,6 +759,8 @@ def main() -> int:
                     help="with --design: no measurement, just two steps of that kind of one block of layers, kernel by "
                          "kernel, for a profiler to capture")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")
+    ap.add_argument("--arm", default="design", choices=["design", "other"],
+                    help="with --design and --profile: the design itself, or the model it is compared with")
     ap.add_argument("--batches", default="1,8,64", help="with --design: decode batch sizes")
     args = ap.parse_args()
 

@@ -192,4 +192,22 @@ __device__ __forceinline__ float silu_fast(float x) {
     return x * rcp_approx(1.f + ex2_approx(-1.44269504f * x));
 }
 
+// The clamped gated form (activation code 2 of the products' gated epilogues): g = min(g, limit), u = clamp(u, -limit,
+// limit) (limit <= 0: no clamp), g logistic(1.702 g) (u + 1).
+constexpr float kSwishAlpha = 1.702f;
+__device__ __forceinline__ float clamped_swish(float g, float u, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g / (1.f + expf(-kSwishAlpha * g)) * (u + 1.f);
+}
+__device__ __forceinline__ float clamped_swish_fast(float g, float u, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g * rcp_approx(1.f + ex2_approx(-1.44269504f * kSwishAlpha * g)) * (u + 1.f);
+}
+
 }  // namespace hos

@@ -71,8 +71,12 @@ gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __rest
             float v = acc[i][j];
             if (EPI == kEpiSoftcap) v = softcap_precise(v, cap);
             if (EPI == kEpiGated) {
-                const float a = act == 0 ? gelu_tanh(v) : v / (1.f + expf(-v));
-                v = a * acc_u[i][j];
+                if (act == 2) {
+                    v = clamped_swish(v, acc_u[i][j], cap);          // the clamp's limit rides in `cap`
+                } else {
+                    const float a = act == 0 ? gelu_tanh(v) : v / (1.f + expf(-v));
+                    v = a * acc_u[i][j];
+                }
             }
             out[(size_t)m * ldo + n] = from_float<TO>(v);
         }

@@ -55,7 +55,8 @@ __device__ __forceinline__ uint4 ldg16_stream(const bf16* p) {
 template <int MT, int kUnroll, bool GATED, typename OutT, int WARPS = kSkinnyWarps>
 __global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ out,
-                   int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act, int late) {
+                   int M, int N, int K, int lda, int ldw, int ldo, int gate_rows, int act, int late,
+                   float act_limit) {
     // The kernel may be launched ahead of the end of the kernel before it: its CTAs are placed and a warp's first
     // round of weights, which no kernel writes, is on its way before the activations exist.
     // (`late`: the kernel after this one is let go only when the kernel before this one has ended: this kernel was
@@ -161,8 +162,12 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             float gsum = 0.f, usum = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS / 2; ++w) { gsum += part[w][m][r][t]; usum += part[WARPS / 2 + w][m][r][t]; }
-            const float a = act == 0 ? gelu_tanh(gsum) : gsum / (1.f + __expf(-gsum));
-            v = a * usum;
+            if (act == 2) {
+                v = clamped_swish_fast(gsum, usum, act_limit);
+            } else {
+                const float a = act == 0 ? gelu_tanh(gsum) : gsum / (1.f + __expf(-gsum));
+                v = a * usum;
+            }
         } else {
             v = 0.f;
 #pragma unroll
@@ -354,12 +359,13 @@ static bool skinny_ahead(int kind) { return (skinny_ahead_mode() & kind) != 0 ||
 // everywhere else (2, 4 or 8 sequences; one sequence at 32,768 keys): it stays behind its attention kernel.
 
 // out[M, N] = A[M, K] . W[N, K]^T for M <= 32.  epilogue 0: none (out bf16 or f32); 2: gated (W has
-// 2N rows: gate rows, then up rows at row N; out bf16).  K and the leading dimensions must be
+// 2N rows: gate rows, then up rows at row N; out bf16; act 0, 1, or 2, the clamped form with its limit in act_limit).
+// K and the leading dimensions must be
 // multiples of 8 elements, A and W 16-byte aligned.
 // k_splits > 1: `out` is [k_splits][M][ldo] 32-bit partial sums for a consumer that adds them (no epilogue).
 extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_dtype, int M, int N, int K,
-                               int lda, int ldw, int ldo, int epilogue, int act, int k_splits, int room_before,
-                               cudaStream_t stream) {
+                               int lda, int ldw, int ldo, int epilogue, int act, float act_limit, int k_splits,
+                               int room_before, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 8 * kMaxTokenTiles) HOS_REFUSE("gemm_skinny: %d rows are more than %d", M, 8 * kMaxTokenTiles);
     if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A % 16) || ((uintptr_t)W % 16))
@@ -385,7 +391,7 @@ extern "C" int hos_gemm_skinny(const void* A, const void* W, void* out, int out_
     const int late = (kind == 2 || kind == 4) && ahead ? 1 : 0;     // o and down, when launched ahead
 #define HOS_SK_W(MT, U, G, T, WP)                                                                                \
     launch_ahead(ahead, gemm_skinny_kernel<MT, U, G, T, WP>, dim3(grid, k_splits), dim3(WP * 32), 0, stream, (const bf16*)A, (const bf16*)W, (T*)out, \
-                                                                       M, N, K, lda, ldw, ldo, N, act, late)
+                                                                       M, N, K, lda, ldw, ldo, N, act, late, act_limit)
 #define HOS_SK(MT, U, G, T) HOS_SK_W(MT, U, G, T, (G ? kGatedWarps : kSkinnyWarps))
 #define HOS_SK_U(MT, G, T)                              \
     do {                                                \

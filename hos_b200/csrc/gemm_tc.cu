@@ -155,8 +155,8 @@ struct GemmParams {
     int ldo;
     int k_splits;
     int gate_rows;        // gated: row of W where the up rows begin
-    float cap;
-    int act;
+    float cap;            // the soft-cap; with the gated epilogue's activation 2, the clamp's limit
+    int act;              // gated: 0 tanh-form GELU, 1 x logistic(x), 2 the clamped form (common.cuh)
     RopeEpi rope;         // kGEpiRope only
 };
 
@@ -319,6 +319,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                             if (p.act == 0) {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) f[j] = gelu_tanh_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
+                            } else if (p.act == 2) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) f[j] = clamped_swish_fast(__uint_as_float(v[j]), __uint_as_float(u[j]), p.cap);
                             } else {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) f[j] = silu_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
@@ -384,6 +387,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_m,     // the 128-row ope
                             if (p.act == 0) {
 #pragma unroll
                                 for (int j = 0; j < CH; ++j) f[j] = gelu_tanh_fast(f[j]) * exchange[r * BN + c0 + j];
+                            } else if (p.act == 2) {
+#pragma unroll
+                                for (int j = 0; j < CH; ++j) f[j] = clamped_swish_fast(f[j], exchange[r * BN + c0 + j], p.cap);
                             } else {
 #pragma unroll
                                 for (int j = 0; j < CH; ++j) f[j] = silu_fast(f[j]) * exchange[r * BN + c0 + j];
@@ -727,6 +733,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,     // A: boxes o
                         if (p.act == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = gelu_tanh_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);
+                        } else if (p.act == 2) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = clamped_swish_fast(__uint_as_float(v[j]), __uint_as_float(u[j]), p.cap);
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = silu_fast(__uint_as_float(v[j])) * __uint_as_float(u[j]);

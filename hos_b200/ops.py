@@ -22,8 +22,10 @@ from .errors import KernelError
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
 EPI_NONE, EPI_SOFTCAP, EPI_GATED = 0, 1, 2
-ACT_GELU_TANH, ACT_SILU = 0, 1
+ACT_GELU_TANH, ACT_SILU, ACT_CLAMPED_SWISH = 0, 1, 2
 ACTIVATIONS = {"gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+# the clamped form as the products' gated epilogues know it: g logistic(SWISH_ALPHA g) (u + SWISH_SHIFT), the limit a parameter
+SWISH_ALPHA, SWISH_SHIFT = 1.702, 1.0
 ROPE_STYLES = {"rotate_half": 0, "interleaved": 1}
 
 _p, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong

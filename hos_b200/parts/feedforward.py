@@ -6,8 +6,10 @@ is never written.
 
 "clamped_swish" is the form g = min(gate(h), limit), u = clamp(up(h), -limit, limit), down(g logistic(alpha g)
 (u + up_shift)) with `limit`, `alpha` (1.702 by default) and `up_shift` (1 by default) as parameters: the form the
-routed experts' kernels know, for a dense layer.  Gate and up come out of one product as 32-bit rows; the clamp, the
-activation and the product are 32-bit and rounded once."""
+routed experts' kernels know, for a dense layer.  With the usual constants (alpha 1.702, up_shift 1) it is the third
+activation of the products' gated epilogues, the limit a parameter; with other constants gate and up come out of one
+product as 32-bit rows and a kernel of its own takes the clamp, the activation and the product.  Both ways the clamp,
+the activation and the product are 32-bit and rounded once."""
 from __future__ import annotations
 
 from typing import List, Mapping
@@ -23,6 +25,7 @@ from .base import FeedForward, StepInfo, WeightSpec
 
 class GatedMLP(FeedForward):
     graph_safe = True
+    fused = True          # tests switch it off to compare the clamped form's two ways
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -54,6 +57,8 @@ class GatedMLP(FeedForward):
     def _inner(self, h: torch.Tensor) -> torch.Tensor:
         if not self.clamped:
             return linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=self.act)
+        if self.fused and self.alpha == ops.SWISH_ALPHA and self.up_shift == ops.SWISH_SHIFT:
+            return linear.matmul(h, self.w_gate_up, epilogue=ops.EPI_GATED, act=ops.ACT_CLAMPED_SWISH, cap=self.limit)
         gu = linear.matmul(h, self.w_gate_up, out_dtype=torch.float32)
         z = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
         ops.clamped_gated_act(gu, z, self.limit, self.alpha, self.up_shift)

@@ -27,7 +27,8 @@ def plain_forced() -> bool:
 def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            epilogue: int = ops.EPI_NONE, cap: float = 0.0, act: int = 0,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N or 2N, K]^T (2N rows with the gated epilogue)."""
+    """out[M, N] = x[M, K] . w[N or 2N, K]^T (2N rows with the gated epilogue; with its clamped activation the limit
+    rides in `cap`)."""
     m = x.shape[0]
     n = w.shape[0] // 2 if epilogue == ops.EPI_GATED else w.shape[0]
     if out is None:
@@ -37,7 +38,7 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if (not _force_plain and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
         from . import gemm_skinny, gemm_tc
         if gemm_skinny.can_take(x, w, out, epilogue):
-            gemm_skinny.matmul(x, w, out, epilogue, act)
+            gemm_skinny.matmul(x, w, out, epilogue, act, cap)
             return out
         if gemm_tc.can_take(x, w, out, epilogue):
             gemm_tc.matmul(x, w, out, epilogue, cap, act)

@@ -543,3 +543,56 @@ def test_the_small_kernels_alone_against_float64():
     assert torch.equal(choice.cpu().view(n, top).long(), best.indices)
     want = best.values / (best.values.sum(-1, keepdim=True) + 1e-20) * 2.5
     assert float((weight.double().cpu().view(n, top) - want).abs().max()) < 1e-5
+
+
+def test_the_clamped_form_in_the_products_epilogues():
+    """The dense feed-forward's clamp, activation and product as the third activation of the gated epilogues: the
+    few-rows kernel, the tcgen05 kernel in both orientations and on pairs of SMs, the plain kernel in both types,
+    against float64; and the part's two ways (fused, or a kernel of its own) on the same rows."""
+    from hos_b200 import ops
+    from hos_b200.parts import linear
+    dev = "cuda"
+    torch.manual_seed(9)
+    k, f, limit = 256, 384, 0.9
+    w = (torch.randn(2 * f, k, device=dev) * 0.08).to(torch.bfloat16)
+    for m in (1, 5, 24, 100, 300, 1100):
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        gu = x.double().cpu() @ w.double().cpu().T
+        g, u = gu[:, :f].clamp(max=limit), gu[:, f:].clamp(-limit, limit)
+        want = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+        got = linear.matmul(x, w, epilogue=ops.EPI_GATED, act=ops.ACT_CLAMPED_SWISH, cap=limit)
+        assert got.dtype == torch.bfloat16
+        assert float((got.double().cpu() - want).abs().max()) < 2e-2 * max(1.0, float(want.abs().max())), f"{m} rows"
+        linear.force_plain(True)
+        try:
+            got = linear.matmul(x, w, epilogue=ops.EPI_GATED, act=ops.ACT_CLAMPED_SWISH, cap=limit)
+            got32 = linear.matmul(x.float(), w.float(), epilogue=ops.EPI_GATED, act=ops.ACT_CLAMPED_SWISH, cap=limit)
+        finally:
+            linear.force_plain(False)
+        assert float((got.double().cpu() - want).abs().max()) < 2e-2 * max(1.0, float(want.abs().max()))
+        assert float((got32.double().cpu() - want).abs().max()) < 1e-5 * max(1.0, float(want.abs().max()))
+        # no clamp at all: the limit is zero
+        free = gu[:, :f] * torch.sigmoid(1.702 * gu[:, :f]) * (gu[:, f:] + 1.0)
+        got = linear.matmul(x, w, epilogue=ops.EPI_GATED, act=ops.ACT_CLAMPED_SWISH, cap=0.0)
+        assert float((got.double().cpu() - free).abs().max()) < 2e-2 * max(1.0, float(free.abs().max()))
+
+
+def test_the_dense_feed_forward_fused_and_in_two_steps(folders):
+    from hos_b200.parts.feedforward import GatedMLP
+    vocab = CASES["A"][0]["vocab"]
+    seq = tokens(160, 200, vocab)
+    want = _oracle(folders["A"], [seq])[0]
+    for dtype in ("float32", "bfloat16"):
+        outs = []
+        for fused in (True, False):
+            GatedMLP.fused = fused
+            try:
+                r = _runner(folders["A"], dtype)
+                (slot,) = r.admit(1)
+                got = [r.step([slot], [seq[:190]], [list(range(190))])] + [r.step([slot], [[t]]) for t in seq[190:]]
+                outs.append(torch.cat(got).cpu())
+                r.release(slot)
+            finally:
+                GatedMLP.fused = True
+        for o in outs:
+            assert_rows(o, want, dtype, "the clamped feed-forward")
