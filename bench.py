@@ -496,20 +496,20 @@ TOFODRA_SIZES = {
 
 def tofodra_raw(z):
     dense = {"kind": "dense", "ff": z["dense_ff"], "limit": 7.0}
-    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5},
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.0},
            "shared": {"ff": z["shared"]}}
     lat = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["lat_rot"], "vdim": z["lat_vdim"], "kv_rank": z["rank"],
            "scale": (z["lat_dim"] + z["lat_rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["lat_rot"]}}
     ret = {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_vdim"], "rot": {"base": 10000.0, "dims": z["ret_dim"]},
            "decay": [1.0 - 2.0 ** -(5 + 5 * i / max(1, z["ret_heads"] - 1)) for i in range(z["ret_heads"])]}
     att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
-           "diff": 0.6, "mask": {"size": z["window"], "keep_first": z["keep"]}}
+           "diff": 0.5, "mask": {"size": z["window"], "keep_first": z["keep"]}}
     layers = []
     for b in range(z["blocks"]):
         layers += [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "retention", "mixer": ret, "mlp": moe},
                    {"type": "attention", "mixer": att, "mlp": dense},
                    {"type": "latent_attention", "mixer": dict(lat, kv_from=4 * b), "mlp": moe}]
-    return {"architecture": "Tofodra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+    return {"architecture": "Tofodra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
             "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": layers}
 
 

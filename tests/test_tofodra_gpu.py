@@ -205,7 +205,7 @@ def test_far_keys_kept_keys_and_a_long_memory(tmp_path):
                          latent(3, 4, 4, 8, 16, 0.12, kv_from=0, mlp=None)])
     folder = make_folder(tmp_path, raw, 5, "far")
     cfg, w = oracle_view(folder)
-    seq = tokens(70, 640, 60)
+    seq = tokens(70, 644, 60)
     want = P.forward(cfg, w, seq)
 
     def no_far(i, m):
@@ -533,15 +533,15 @@ def test_the_small_kernels_alone_against_float64():
         ops.clamped_gated_act(gu, out, limit, alpha, shift)
         assert float((out.double().cpu() - want).abs().max()) < 1e-5
     h = torch.randn(n, 64, device=dev)
-    router = torch.randn(12, 64, device=dev) * 0.3
-    top = 3
+    router = torch.randn(10, 64, device=dev) * 0.3
+    top = 4
     choice = torch.empty(n * top, dtype=torch.int32, device=dev)
     weight = torch.empty(n * top, dtype=torch.float32, device=dev)
-    ops.moe_route(h, router, None, seq, choice, weight, top, ops.MOE_SCORING["logistic"], 1e-20, 2.5)
+    ops.moe_route(h, router, None, seq, choice, weight, top, ops.MOE_SCORING["logistic"], 1e-20, 1.75)
     s = torch.sigmoid(h.double().cpu() @ router.double().cpu().T)
     best = torch.topk(s, top, dim=-1)
     assert torch.equal(choice.cpu().view(n, top).long(), best.indices)
-    want = best.values / (best.values.sum(-1, keepdim=True) + 1e-20) * 2.5
+    want = best.values / (best.values.sum(-1, keepdim=True) + 1e-20) * 1.75
     assert float((weight.double().cpu().view(n, top) - want).abs().max()) < 1e-5
 
 

@@ -98,7 +98,7 @@ CASE_E = model(256, 500, [attention(8, 2, 32, 128, 0.25, 0.3, window=300, keep=7
                           latent(16, 16, 16, 24, 200, 0.3),
                           attention(4, 4, 64, 64, 0.2, 0.7, window=64, keep=64, mlp=None),
                           retention((0.9,), 128, 64, rot=32, mlp=moe(9, 1, 72)),
-                          latent(4, 32, 16, 40, 200, 0.25, kv_from=2)], ff=264, limit=1.5, scale=8.0)
+                          latent(4, 32, 16, 40, 200, 0.25, kv_from=2)], ff=264, limit=2.0, scale=8.0)
 CASES = {"A": (CASE_A, 41), "B": (CASE_B, 42), "C": (CASE_C, 43), "D": (CASE_D, 44), "E": (CASE_E, 45)}
 
 
