@@ -90,7 +90,8 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   int aligned, int act_in_walk, const float* __restrict__ g, long long g_ld, const float* __restrict__ beta,
                   long long beta_ld, float* __restrict__ state, const int* __restrict__ token_pos,
                   const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                  float* __restrict__ out, int H, int Gk, int dim, int vdim, int CC) {
+                  float* __restrict__ out, int H, int Gk, int dim, int vdim, int CC, const float* __restrict__ rot_freq,
+                  int rot_dims, int rot_style, float k_mult) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * CC;
@@ -100,6 +101,7 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int kh = head / (H / Gk);
     const int r = threadIdx.x % R, c = threadIdx.x / R;
     const int col = col0 + c;
+    const bool rot_in_walk = rot_dims > 0 || k_mult != 1.f;
     const bool live = c < CC && col < vdim;
     const int dpad = R * (DR + kPad);
     // two buffers of staged tokens: while one chunk is walked the next one's rows are on their way (cp.async)
@@ -171,6 +173,31 @@ state_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         if (t0 + kScanChunk < hi) stage(t0 + kScanChunk, min(kScanChunk, hi - t0 - kScanChunk), sm + (which ^ 1) * per_buf);
         float* qs = sm + which * per_buf;
         float* ks = qs + kScanChunk * dpad;
+        if (rot_in_walk) {
+            // the staged q and k turn with their tokens' positions, and the keys take their factor, as rotate_rows would
+            // have done in a launch of its own (meant for single-token steps: every block of a head repeats it)
+            const int half = rot_dims >> 1, per = half + (dim - rot_dims);
+            for (int idx = threadIdx.x; idx < nt * per; idx += blockDim.x) {
+                const int t = idx / per, j = idx - t * per;
+                float* qp = qs + t * dpad;
+                float* kp = ks + t * dpad;
+                if (j < half) {
+                    const int a = rot_style == 0 ? j : 2 * j, b = rot_style == 0 ? j + half : 2 * j + 1;
+                    const int ia = a + (a / DR) * kPad, ib = b + (b / DR) * kPad;
+                    float sn, cs;
+                    sincosf((float)token_pos[t0 + t] * rot_freq[j], &sn, &cs);
+                    const float qu = qp[ia], qv = qp[ib], ku = kp[ia], kv = kp[ib];
+                    qp[ia] = qu * cs - qv * sn;
+                    qp[ib] = qv * cs + qu * sn;
+                    kp[ia] = (ku * cs - kv * sn) * k_mult;
+                    kp[ib] = (kv * cs + ku * sn) * k_mult;
+                } else {
+                    const int d = rot_dims + (j - half);
+                    kp[d + (d / DR) * kPad] *= k_mult;
+                }
+            }
+            __syncthreads();
+        }
         float* vs = ks + kScanChunk * dpad;
         float* os = vs + kScanChunk * CC;
         float* gs = os + kScanChunk * CC;
@@ -351,12 +378,18 @@ using namespace hos;
 // q, k: rows of Gk heads of `dim` numbers; v: rows of H heads of `vdim`; all float32 with `ld` numbers between rows.
 // g: [.][H] with g_ld between rows (0: one row of constants).  beta: null for the decay rule.  state: [slots][H][vdim][dim].
 // out: float32 [N][H][vdim].  act_in_walk (decay rule only, meant for single-token steps): q, k, v are taken through
-// x logistic(x) as they are read, instead of by hos_act_rows before.
+// x logistic(x) as they are read, instead of by hos_act_rows before.  rot_freq ([rot_dims / 2], or null), rot_style, k_mult:
+// the staged q and k are turned by their tokens' positions and the keys multiplied, as hos_rotate_rows would have done
+// before (meant for single-token steps; it follows the rows as they are, so it does not go with act_in_walk).
 extern "C" int hos_state_scan(const float* q, const float* k, const float* v, long long ld, int act_in_walk, const float* g,
                               long long g_ld, const float* beta, long long beta_ld, float* state, const int* token_pos,
                               const int* token_seq, const int* cu_seqlens, const int* seq_slot, float* out, int n_rows,
-                              int n_seqs, int H, int Gk, int dim, int vdim, cudaStream_t stream) {
+                              int n_seqs, int H, int Gk, int dim, int vdim, const float* rot_freq, int rot_dims, int rot_style,
+                              float k_mult, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
+    if (rot_freq == nullptr) rot_dims = 0;
+    if (rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > dim || (rot_style != 0 && rot_style != 1))
+        HOS_REFUSE("state_scan: %d rotated numbers in heads of %d", rot_dims, dim);
     if (Gk <= 0 || H % Gk != 0) HOS_REFUSE("state_scan: %d heads are not a multiple of %d key heads", H, Gk);
     if (dim <= 0 || dim > 1024 || vdim <= 0) HOS_REFUSE("state_scan: heads of %d x %d", dim, vdim);
     // short runs of rows per thread: a token's walk is a chain of dependent instructions (scale, dot, sum over the
@@ -388,7 +421,8 @@ extern "C" int hos_state_scan(const float* q, const float* k, const float* v, lo
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(state_scan_kernel<DRv, Rv, DL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_pdl(state_scan_kernel<DRv, Rv, DL>, grid, dim3(threads), smem, stream, q, k, v, ld, aligned, act_in_walk, g, g_ld, beta, \
-                   beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, CC);           \
+                   beta_ld, state, token_pos, token_seq, cu_seqlens, seq_slot, out, H, Gk, dim, vdim, CC, rot_freq,  \
+                   rot_dims, rot_style, k_mult);                                                                     \
     } while (0)
 #define HOS_SCAN_D(DRv, Rv)                                                                                          \
     do {                                                                                                             \

@@ -1019,8 +1019,9 @@ def gated_attn_mma_decode(q: torch.Tensor, cache: PagedKVArgs, sink: Optional[to
 
 def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_load: bool, g: torch.Tensor,
                per_token_g: bool, beta: Optional[torch.Tensor], state: torch.Tensor, step, out: torch.Tensor,
-               heads: int, key_heads: int, dim: int, vdim: int) -> None:
-    """The matrix-state recurrence over the step's sequences.  rows: float32 [N, ld] holding q, k (key_heads x dim) and
+               heads: int, key_heads: int, dim: int, vdim: int, rot=None) -> None:
+    """The matrix-state recurrence over the step's sequences.  rot = (freq, rot_dims, style, k_mult): q and k turn with
+    their positions and the keys take a factor inside the walk (single-token steps), instead of by rotate_rows before.  rows: float32 [N, ld] holding q, k (key_heads x dim) and
     v (heads x vdim) from the given columns on.  g: [heads] constants, or [N, heads] per token; beta ([N, heads]): the
     delta rule, None: the plain decay rule.  state: [slots, heads, vdim, dim] float32.  out: float32 [N, heads * vdim]."""
     _check(rows, "recurrence inputs", torch.float32, 2)
@@ -1031,6 +1032,8 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
     if out.shape != (n, heads * vdim) or tuple(state.shape[1:]) != (heads, vdim, dim):
         raise KernelError("state_scan: sizes disagree")
     base = rows.data_ptr()
+    if rot is not None and (silu_on_load or beta is not None or key_heads != heads):
+        raise KernelError("state_scan: the rotation in the walk goes with the plain decay rule on rows as they are")
     in_walk = bool(silu_on_load) and beta is None and step.max_new == 1      # single tokens: no launch of its own for it
     if silu_on_load and not in_walk:        # q, k, v lie side by side from q_col on: x logistic(x) in place, once, before the walk
         if not (q_col < k_col < v_col) or v_col + heads * vdim - q_col != 2 * key_heads * dim + heads * vdim:
@@ -1040,7 +1043,8 @@ def state_scan(rows: torch.Tensor, q_col: int, k_col: int, v_col: int, silu_on_l
                   ctypes.c_void_p(base + 4 * v_col), ld, 1 if in_walk else 0, _ptr(g), heads if per_token_g else 0,
                   _ptr(beta), heads if beta is not None else 0, _ptr(state), _ptr(step.token_pos), _ptr(step.token_seq),
                   _ptr(step.cu_seqlens), _ptr(step.seq_slot), _ptr(out), n, int(step.n_seqs), int(heads), int(key_heads),
-                  int(dim), int(vdim), _stream())
+                  int(dim), int(vdim), _ptr(rot[0]) if rot else None, int(rot[1]) if rot else 0, int(rot[2]) if rot else 0,
+                  float(rot[3]) if rot else 1.0, _stream())
 
 
 def act_rows(rows: torch.Tensor, cols: int) -> None:

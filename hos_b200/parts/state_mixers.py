@@ -93,14 +93,18 @@ class DecayLinearAttention(Mixer):
         proj = linear.matmul(h, self.w_in, out_dtype=torch.float32)
         o = torch.empty((n, self.v_cols), dtype=torch.float32, device=h.device)
         turns = self.position is not None or self.key_scale != 1.0
+        rot = None
         if turns:
             # the rotation follows the activation, so the activation cannot ride in the scan's walk here
             if self.activates:
                 ops.act_rows(proj, 2 * self.qk_cols + self.v_cols)
             freq, rot_dims, style = self.position.kernel_args() if self.position else (None, 0, 0)
-            ops.rotate_rows(proj, self.n_heads, self.n_heads, self.dim, freq, rot_dims, style, step, self.key_scale)
+            if step.max_new == 1 and not self.activates:
+                rot = (freq, rot_dims, style, self.key_scale)       # single tokens: the scan turns what it stages
+            else:
+                ops.rotate_rows(proj, self.n_heads, self.n_heads, self.dim, freq, rot_dims, style, step, self.key_scale)
         ops.state_scan(proj, 0, self.qk_cols, 2 * self.qk_cols, self.activates and not turns, self.decay_t, False, None,
-                       store.state["S"], step, o, self.n_heads, self.n_heads, self.dim, self.vdim)
+                       store.state["S"], step, o, self.n_heads, self.n_heads, self.dim, self.vdim, rot=rot)
         y = torch.empty((n, self.v_cols), dtype=h.dtype, device=h.device)
         if self.norm_per_head:
             ops.group_norm_gate(o, self.norm_w, proj, 2 * self.qk_cols + self.v_cols, self.gate_act, step.token_seq, y,
